@@ -1,0 +1,174 @@
+"""Operators over packed weights: thin, checked calls into libjq.so.
+
+Everything here runs on the GPU through the C ABI; there is no eager or CPU
+fallback.  The fused linear is also registered as ``torch.ops.jq.linear`` so
+that it composes with torch's dispatcher (fake tensors, export).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+from .pack import PackedWeight
+from .spec import QuantSpec
+
+_DT = {torch.float32: _lib.JQ_F32, torch.float16: _lib.JQ_F16, torch.bfloat16: _lib.JQ_BF16}
+MAX_GEMV_BATCH = 8
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("libjq operators run on CUDA tensors only (there is no CPU path)")
+
+
+def dequantize(pw: PackedWeight) -> torch.Tensor:
+    """Dense fp32 [N, K] of a packed matrix (bit-exact definition of W_hat)."""
+    lib = _lib.load()
+    _need_cuda(pw.qweight, pw.scales, pw.codebook)
+    out = torch.empty((pw.N, pw.K), dtype=torch.float32, device=pw.qweight.device)
+    with torch.cuda.device(out.device):
+        if pw.spec.fmt == "e2m1":
+            st = lib.jq_dequant_e2m1(_ptr(pw.qweight), _ptr(pw.scales), _ptr(out), pw.N, pw.K, pw.spec.group_size,
+                                     _stream())
+        else:
+            st = lib.jq_dequant_gf4(_ptr(pw.qweight), _ptr(pw.scales), _ptr(pw.codebook), _ptr(out), pw.N, pw.K,
+                                    pw.spec.group_size, _stream())
+    _lib.check(st, "jq_dequant")
+    return out
+
+
+def fwht_block(x: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """fp32 block Hadamard rotation along the last dim."""
+    lib = _lib.load()
+    _need_cuda(x)
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    y = torch.empty(x2.shape, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        st = lib.jq_fwht_block(_ptr(x2), _ptr(y), x2.shape[0], x2.shape[1], block, _DT[x2.dtype], _stream())
+    _lib.check(st, "jq_fwht_block")
+    return y.reshape(x.shape)
+
+
+_OUT = {-1: None, _lib.JQ_F32: torch.float32, _lib.JQ_F16: torch.float16, _lib.JQ_BF16: torch.bfloat16}
+
+
+def _linear_rows(x2, qweight, scales, codebook, bias, fmt_id, N, K, g, had, out_id=-1):
+    lib = _lib.load()
+    Bt = x2.shape[0]
+    y = torch.empty((Bt, N), dtype=_OUT[out_id] or x2.dtype, device=x2.device)
+    with torch.cuda.device(x2.device):
+        for b0 in range(0, Bt, MAX_GEMV_BATCH):
+            b1 = min(Bt, b0 + MAX_GEMV_BATCH)
+            xs, ys = x2[b0:b1], y[b0:b1]
+            if fmt_id == _lib.JQ_FMT_E2M1:
+                st = lib.jq_gemv_e2m1(_ptr(qweight), _ptr(scales), _ptr(xs), _ptr(bias), _ptr(ys), N, K, b1 - b0, g,
+                                      had, _DT[x2.dtype], _DT[y.dtype], None, 0, _stream())
+            else:
+                st = lib.jq_gemv_gf4(_ptr(qweight), _ptr(scales), _ptr(codebook), _ptr(xs), _ptr(bias), _ptr(ys), N,
+                                     K, b1 - b0, g, had, _DT[x2.dtype], _DT[y.dtype], None, 0, _stream())
+            _lib.check(st, "jq_gemv")
+    return y
+
+
+@torch.library.custom_op("jq::linear", mutates_args=(), device_types="cuda")
+def _jq_linear(x: torch.Tensor, qweight: torch.Tensor, scales: Optional[torch.Tensor],
+               codebook: Optional[torch.Tensor], bias: Optional[torch.Tensor], fmt_id: int, N: int, K: int,
+               group_size: int, had_block: int, out_id: int) -> torch.Tensor:
+    x2 = x.reshape(-1, K).contiguous()
+    y = _linear_rows(x2, qweight, scales, codebook, bias, fmt_id, N, K, group_size, had_block, out_id)
+    return y.reshape(*x.shape[:-1], N)
+
+
+@_jq_linear.register_fake
+def _(x, qweight, scales, codebook, bias, fmt_id, N, K, group_size, had_block, out_id):
+    return x.new_empty((*x.shape[:-1], N), dtype=_OUT[out_id] or x.dtype)
+
+
+def linear(x: torch.Tensor, pw: PackedWeight, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``F.linear(rotate(x), W_hat, bias)`` without materialising W_hat; any
+    leading dims, last dim = K; output dtype = input dtype unless given."""
+    if x.shape[-1] != pw.K:
+        raise RuntimeError(f"last dim of x is {x.shape[-1]}, packed weight has K={pw.K}")
+    if x.dtype not in _DT:
+        raise RuntimeError(f"unsupported activation dtype {x.dtype}")
+    _need_cuda(x, pw.qweight, pw.scales, pw.codebook, bias)
+    if bias is not None and bias.dtype != torch.float32:
+        bias = bias.float()
+    return torch.ops.jq.linear(x, pw.qweight, pw.scales, pw.codebook, bias, pw.spec.fmt_id, pw.N, pw.K,
+                               pw.spec.group_size, pw.spec.had_block, -1 if out_dtype is None else _DT[out_dtype])
+
+
+class GroupedGemv:
+    """A fixed set of independent GEMVs (one decode step's matrices) run in a
+    single launch.  Inputs and outputs are preallocated; ``run()`` only
+    enqueues the kernel."""
+
+    def __init__(self, weights: Sequence[PackedWeight], batch: int, x_dtype=torch.bfloat16,
+                 biases: Optional[Sequence[Optional[torch.Tensor]]] = None, device=None):
+        lib = _lib.load()
+        if not weights:
+            raise ValueError("no problems")
+        spec0 = weights[0].spec
+        for w in weights:
+            if w.spec.fmt != spec0.fmt:
+                raise ValueError("a grouped launch needs one weight format")
+        self.device = device or weights[0].qweight.device
+        self.weights = list(weights)
+        self.batch = batch
+        self.x_dtype = x_dtype
+        self.biases = list(biases) if biases is not None else [None] * len(weights)
+        # all inputs live in one arena and all outputs in another, so a step's
+        # activations move with one copy each way; every view is 256-byte aligned
+        esz = torch.empty((), dtype=x_dtype).element_size()
+        rnd = lambda nbytes: (nbytes + 255) // 256 * 256
+        x_off, y_off, xo, yo = [], [], 0, 0
+        for w in weights:
+            x_off.append(xo); xo += rnd(batch * w.K * esz)
+            y_off.append(yo); yo += rnd(batch * w.N * esz)
+        self.x_arena = torch.zeros(xo, dtype=torch.uint8, device=self.device)
+        self.y_arena = torch.zeros(yo, dtype=torch.uint8, device=self.device)
+        self.x_offsets, self.y_offsets = x_off, y_off
+        self.xs: List[torch.Tensor] = [
+            self.x_arena[o:o + batch * w.K * esz].view(x_dtype).view(batch, w.K) for o, w in zip(x_off, weights)]
+        self.ys: List[torch.Tensor] = [
+            self.y_arena[o:o + batch * w.N * esz].view(x_dtype).view(batch, w.N) for o, w in zip(y_off, weights)]
+        n = len(weights)
+        arr = (_lib.jq_problem * n)()
+        for i, w in enumerate(weights):
+            arr[i].qweight = w.qweight.data_ptr()
+            arr[i].scales = w.scales.data_ptr() if w.scales is not None else None
+            arr[i].codebook = w.codebook.data_ptr() if w.codebook is not None else None
+            arr[i].x = self.xs[i].data_ptr()
+            arr[i].bias = self.biases[i].data_ptr() if self.biases[i] is not None else None
+            arr[i].y = self.ys[i].data_ptr()
+            arr[i].N, arr[i].K, arr[i].g, arr[i].had_block = w.N, w.K, w.spec.group_size, w.spec.had_block
+        self._problems_host = arr
+        with torch.cuda.device(self.device):
+            nbytes = lib.jq_grouped_plan_bytes(n)
+            self._plan_host = np.zeros((nbytes + 3) // 4, dtype=np.int32)
+            _lib.check(lib.jq_grouped_plan(spec0.fmt_id, ctypes.byref(arr), n, batch, self._plan_host.ctypes.data,
+                                           self._plan_host.nbytes), "jq_grouped_plan")
+            raw = np.frombuffer(bytes(arr), dtype=np.uint8).copy()
+            self._problems_dev = torch.from_numpy(raw).to(self.device)
+            self._plan_dev = torch.from_numpy(self._plan_host).to(self.device)
+
+    def run(self) -> None:
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            st = lib.jq_gemv_grouped(_ptr(self._problems_dev), self._plan_host.ctypes.data, _ptr(self._plan_dev),
+                                     _DT[self.x_dtype], _DT[self.x_dtype], _stream())
+        _lib.check(st, "jq_gemv_grouped")

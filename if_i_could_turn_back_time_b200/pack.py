@@ -1,0 +1,71 @@
+"""Host-side packers: fp32 weight matrix -> packed 4-bit tensors.
+
+These take the place of the grid construction in the reference's
+``QuantLinear.__init__`` (Python_Jenks_Test/Jenks_Tests/Quantization_Experiments/
+layers.py:22-26: per-row scale, integer grid) for the packed formats.  The
+arithmetic runs in the native library (multi-threaded C++); this module only
+marshals tensors.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+from .spec import QuantSpec, row_stride_codes
+
+
+@dataclass
+class PackedWeight:
+    """A packed [N, K] weight matrix (tensors may live on any device)."""
+    spec: QuantSpec
+    N: int
+    K: int
+    qweight: torch.Tensor                 # uint8 [N, stride/2]
+    scales: Optional[torch.Tensor]        # fp16 [N, K/g] or None
+    codebook: Optional[torch.Tensor]      # fp16 [N, 16] (gf4) or None
+
+    def to(self, device) -> "PackedWeight":
+        mv = lambda t: None if t is None else t.to(device).contiguous()
+        return PackedWeight(self.spec, self.N, self.K, mv(self.qweight), mv(self.scales), mv(self.codebook))
+
+    def rows(self, lo: int, hi: int) -> "PackedWeight":
+        """Row shard [lo, hi): everything in the format is per row."""
+        sl = lambda t: None if t is None else t[lo:hi].contiguous()
+        return PackedWeight(self.spec, hi - lo, self.K, sl(self.qweight), sl(self.scales), sl(self.codebook))
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.qweight, self.scales, self.codebook) if t is not None)
+
+
+def pack_weight(W: torch.Tensor, spec: QuantSpec, threads: int = 0, rotate: bool = True) -> PackedWeight:
+    """Quantise and pack W [N, K].  With ``spec.had_block`` the weight is first
+    multiplied on the right by the block Hadamard matrix (fp32), so that
+    ``W x == (W H)(H x)`` once the operator rotates x."""
+    lib = _lib.load()
+    Wf = W.detach().to("cpu", torch.float32).contiguous().clone()
+    N, K = Wf.shape
+    g = spec.group_size
+    if g and K % g:
+        raise ValueError(f"K={K} is not a multiple of the group size {g}")
+    if spec.had_block and K % spec.had_block:
+        raise ValueError(f"K={K} is not a multiple of the rotation block {spec.had_block}")
+    wn = Wf.numpy()
+    if spec.had_block and rotate:
+        _lib.check(lib.jq_rotate_weights_host(wn.ctypes.data, N, K, spec.had_block, threads), "jq_rotate_weights_host")
+    q = np.zeros((N, row_stride_codes(K) // 2), dtype=np.uint8)
+    s = np.zeros((N, K // g), dtype=np.uint16) if g else None
+    if spec.fmt == "e2m1":
+        _lib.check(lib.jq_pack_e2m1_host(wn.ctypes.data, N, K, g, q.ctypes.data, s.ctypes.data, threads),
+                   "jq_pack_e2m1_host")
+        cb = None
+    else:
+        cb = np.zeros((N, 16), dtype=np.uint16)
+        _lib.check(lib.jq_pack_gf4_host(wn.ctypes.data, N, K, g, q.ctypes.data,
+                                        s.ctypes.data if s is not None else None, cb.ctypes.data, threads),
+                   "jq_pack_gf4_host")
+    as_half = lambda a: None if a is None else torch.from_numpy(a.view(np.float16).copy())
+    return PackedWeight(spec, N, K, torch.from_numpy(q), as_half(s), as_half(cb))

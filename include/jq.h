@@ -1,0 +1,167 @@
+/* jq.h -- C ABI of libjq.so: packed 4-bit (E2M1 / GF4) dequantise-and-multiply
+ * for NVIDIA B200 (sm_100a).
+ *
+ * The library slots in under the quantized-Linear forward of
+ * jvap2/If_I_could_turn_back_time, replacing the per-call
+ *     W_bar = mask * s * (Q + Theta);  y = F.linear(x, W_bar, bias)
+ * of Python_Jenks_Test/Jenks_Tests/Quantization_Experiments/layers.py:33-38
+ * (and the same F.linear boundary at Quantization_Experiments/brecq.py:321-329)
+ * by one fused kernel over packed weights.  The reference has no native code
+ * on this path; its only native boundary is a torch C++ extension
+ * (Python_Jenks_Test/Jenks_Tests/cuda_helpers.py:186-211).  Conventions here:
+ *
+ *   - plain C types only; every function returns an int status, 0 = JQ_OK,
+ *     negative = error (jq_strerror gives the text); nothing calls exit(),
+ *     throws, resets the device or synchronises it;
+ *   - the caller owns every buffer; device pointers are raw addresses
+ *     (tensor.data_ptr()); the library allocates no device memory and keeps
+ *     no reference after return;
+ *   - work is enqueued on the CUDA stream passed in (a cudaStream_t cast to
+ *     void*; NULL is the legacy default stream) and returns immediately;
+ *   - arguments are validated on the host before anything is launched.
+ *
+ * Formats.  qweight is uint8 [N, stride/2] row-major, stride = K rounded up to
+ * a multiple of 32 codes (rows are 16-byte multiples); byte j of a row holds
+ * code 2j in bits 3:0 and code 2j+1 in bits 7:4; padding codes are 0.
+ *   E2M1: code = s e1 e0 m, magnitudes {0,.5,1,1.5,2,3,4,6}; scales are fp16
+ *         [N, K/g]; w = fp32(value(code)) * fp32(scale).
+ *   GF4 : code indexes codebook fp16 [N,16] (ascending per row); scales are
+ *         fp16 [N, K/g] or absent (g = 0); w = fp32(codebook[n][code]) *
+ *         fp32(scale)   (or just fp32(codebook[n][code]) when g = 0).
+ * g is 0 (GF4 only) or a multiple of 32 that divides K.
+ */
+#ifndef JQ_H_
+#define JQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define JQ_VERSION 100
+
+/* status codes */
+#define JQ_OK 0
+#define JQ_ERR_NULL_PTR (-1)
+#define JQ_ERR_BAD_SHAPE (-2)
+#define JQ_ERR_BAD_ALIGN (-3)
+#define JQ_ERR_BAD_DTYPE (-4)
+#define JQ_ERR_UNSUPPORTED (-5)
+#define JQ_ERR_WORKSPACE (-6)
+#define JQ_ERR_TIMEOUT (-7)
+#define JQ_ERR_NOMEM (-8)
+#define JQ_ERR_CUDA_BASE (-1000) /* JQ_ERR_CUDA_BASE - cudaError_t */
+
+/* element types of activations / outputs */
+#define JQ_F32 0
+#define JQ_F16 1
+#define JQ_BF16 2
+
+/* weight formats */
+#define JQ_FMT_E2M1 0
+#define JQ_FMT_GF4 1
+
+/* ops for jq_workspace_bytes */
+#define JQ_OP_GEMV 0
+#define JQ_OP_GEMM_TC 1
+#define JQ_OP_GROUPED 2
+
+typedef void *jq_stream_t;
+
+/* Library version (JQ_VERSION of the build).  No reference counterpart. */
+int jq_version(void);
+
+/* Text for a status code; never NULL.  Replaces the bool HandleCUDAError +
+ * exit(1) convention of CUDA_C_Code/include/GPUErrors.cu:3-12. */
+const char *jq_strerror(int status);
+
+/* Dequantise a packed matrix to dense fp32 out[N,K] (row-major, no padding).
+ * Bit-exact: one fp32 multiply per weight.  Replaces the elementwise
+ * "mask * s * (Q + Theta)" materialisation of
+ * Quantization_Experiments/layers.py:37 and QuantLinear.commit (:39-45). */
+int jq_dequant_e2m1(const void *qweight, const void *scales, float *out,
+                    int N, int K, int g, jq_stream_t stream);
+int jq_dequant_gf4(const void *qweight, const void *scales_or_null, const void *codebook,
+                   float *out, int N, int K, int g, jq_stream_t stream);
+
+/* Orthonormal block Walsh-Hadamard rotation of x[B,K] (x_dtype) into fp32
+ * y[B,K]; block must be 128 and divide K.  Fixed butterfly order (strides
+ * 1,2,..,64, a+b low / a-b high, then one multiply by fp32(1/sqrt(128))), so
+ * results are reproducible bit for bit.  No reference counterpart (the
+ * reference has no rotation); it is the stand-alone form of the prologue
+ * fused into jq_gemv_*. */
+int jq_fwht_block(const void *x, float *y, int B, int K, int block, int x_dtype,
+                  jq_stream_t stream);
+
+/* y[B,N] = rotate(x)[B,K] . W_hat[N,K]^T + bias, W_hat never materialised.
+ * Replaces F.linear(x, W_bar, bias) at Quantization_Experiments/layers.py:38
+ * (and :35) for 1 <= B <= 8.  x is row-major [B,K] of x_dtype, y row-major
+ * [B,N] of y_dtype, bias fp32 [N] or NULL.  had_block is 0 (no rotation) or
+ * 128 (K % 128 == 0).  The rotated activation is rounded to fp16 after an
+ * exact power-of-two normalisation per batch row; products are exact and
+ * accumulated in fp32.  workspace may be NULL when jq_workspace_bytes says 0. */
+int jq_gemv_e2m1(const void *qweight, const void *scales, const void *x,
+                 const float *bias_or_null, void *y, int N, int K, int B, int g,
+                 int had_block, int x_dtype, int y_dtype, void *workspace,
+                 size_t workspace_bytes, jq_stream_t stream);
+int jq_gemv_gf4(const void *qweight, const void *scales_or_null, const void *codebook,
+                const void *x, const float *bias_or_null, void *y, int N, int K, int B,
+                int g, int had_block, int x_dtype, int y_dtype, void *workspace,
+                size_t workspace_bytes, jq_stream_t stream);
+
+/* One entry of a grouped launch: an independent GEMV problem. */
+typedef struct jq_problem {
+    const void *qweight;
+    const void *scales;    /* NULL when g == 0 */
+    const void *codebook;  /* NULL for E2M1 */
+    const void *x;
+    const float *bias;     /* NULL for none */
+    void *y;
+    int32_t N, K, g, had_block;
+} jq_problem;
+
+/* Grouped launch: n independent GEMVs (same format, batch B and dtypes) in
+ * ONE launch of persistent CTAs that walk the concatenated row space of all
+ * problems; used for a decode step's layer set, where one launch per matrix
+ * would be bound by launch latency.  Two phases:
+ *   jq_grouped_plan   (host only, once per layer set) validates the problems
+ *       and writes a partition plan of jq_grouped_plan_bytes(n) bytes into
+ *       plan_host; the caller copies those bytes to the device (plan_dev);
+ *   jq_gemv_grouped   enqueues the launch; it reads a few ints of plan_host
+ *       on the host, touches no device memory on the host side and does not
+ *       synchronise.
+ * problems_dev is a DEVICE array of the same n jq_problem given to the plan.
+ * No reference counterpart: the reference runs one F.linear per layer
+ * (Python_Jenks_Test/Jenks_Tests/QuantNetworkTest.py:236-238). */
+size_t jq_grouped_plan_bytes(int n);
+int jq_grouped_plan(int fmt, const jq_problem *problems_host, int n, int B, void *plan_host,
+                    size_t plan_bytes);
+int jq_gemv_grouped(const jq_problem *problems_dev, const void *plan_host, const void *plan_dev,
+                    int x_dtype, int y_dtype, jq_stream_t stream);
+
+/* Bytes of caller-provided device scratch an op needs for these sizes. */
+size_t jq_workspace_bytes(int op, int N, int K, int B);
+
+/* ---- host-side packers (CPU, multi-threaded; one-off, not the hot path) ----
+ * Replace the grid/scale construction of QuantLinear.__init__
+ * (Quantization_Experiments/layers.py:22-26) for the packed formats.  All
+ * pointers are HOST memory.  W is fp32 [N,K] row-major.  qweight receives
+ * [N, stride/2] bytes, scales fp16 bits [N, K/g], codebook fp16 bits [N,16].
+ * threads <= 0 means "all hardware threads". */
+int jq_pack_e2m1_host(const float *W, int N, int K, int g, uint8_t *qweight,
+                      uint16_t *scales, int threads);
+/* GF4: per-row 16-class Jenks natural breaks (the k-class form of the
+ * objective in Python_Jenks_Test/Jenks_Tests/cuda_helpers.py:151-184) on the
+ * group-normalised row; g = 0 means no scales (Jenks on the raw row). */
+int jq_pack_gf4_host(const float *W, int N, int K, int g, uint8_t *qweight,
+                     uint16_t *scales_or_null, uint16_t *codebook, int threads);
+/* In-place right-multiplication of W[N,K] by blockdiag(H_128/sqrt(128)) in
+ * fp32 (the offline weight-side rotation paired with had_block = 128). */
+int jq_rotate_weights_host(float *W, int N, int K, int block, int threads);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JQ_H_ */

@@ -1,0 +1,242 @@
+"""CUDA path vs the CPU oracle, through the C ABI.  Integer / byte results
+(unpacked codes, dequantized weights, the fp32 rotation) must be bit-exact;
+GEMV outputs must satisfy  max|y - y_ref| / max|y_ref| <= 1e-3  against the
+fp32 oracle on identical inputs (TOL below), and a much tighter bound against
+the oracle that also models the kernel's fp16 rounding of the activation."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import if_i_could_turn_back_time_b200 as jq
+from if_i_could_turn_back_time_b200 import ops
+from oracle import formats
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3          # the parity gate
+TOL_MODEL = 3e-6    # same arithmetic, only the fp32 summation order differs
+DEV = "cuda:0"
+
+
+def _oracle_dequant(pw):
+    codes = formats.unpack_nibbles(pw.qweight.cpu().numpy(), pw.K)
+    s = None if pw.scales is None else pw.scales.cpu().numpy()
+    if pw.spec.fmt == "e2m1":
+        return formats.dequant_e2m1(codes, s, pw.spec.group_size)
+    return formats.dequant_gf4(codes, pw.codebook.cpu().numpy(), s, pw.spec.group_size)
+
+
+def _weights(N, K, seed, outliers=True):
+    g = torch.Generator("cpu").manual_seed(seed)
+    W = torch.randn(N, K, generator=g) * 0.02
+    if outliers:
+        W[torch.rand(N, K, generator=g) < 0.001] *= 10
+    return W
+
+
+def _check_gemv(pw, x_cpu, bias_cpu=None):
+    """x_cpu: torch tensor [B,K] of the activation dtype."""
+    pwd = pw.to(DEV)
+    w_hat = _oracle_dequant(pw)
+    x32 = x_cpu.float().numpy()
+    b32 = None if bias_cpu is None else bias_cpu.numpy()
+    y = ops.linear(x_cpu.to(DEV), pwd, None if bias_cpu is None else bias_cpu.to(DEV), out_dtype=torch.float32)
+    y = y.cpu().numpy()
+    ref = formats.linear_ref(x32, w_hat, b32, had_block=pw.spec.had_block)
+    err = formats.rel_err(y, ref)
+    assert err <= TOL, f"rel err {err:.3e} vs fp32 oracle"
+    xm = formats.activation_fp16_model(x32, had=bool(pw.spec.had_block))
+    ref_m = formats.linear_ref(xm, w_hat, b32)
+    err_m = formats.rel_err(y, ref_m)
+    assert err_m <= TOL_MODEL, f"rel err {err_m:.3e} vs fp16-activation model"
+    return err
+
+
+# ---------------------------------------------------------------- dequant ----
+def test_dequant_e2m1_every_byte(golden_dir):
+    z = np.load(os.path.join(golden_dir, "kat_e2m1_bytes.npz"))
+    pw = jq.PackedWeight(jq.QuantSpec("e2m1", 32, 0), 1, 512, torch.from_numpy(z["qweight"]),
+                         torch.ones(1, 16, dtype=torch.float16), None).to(DEV)
+    got = ops.dequantize(pw).cpu().numpy()
+    assert np.array_equal(got, z["values"])
+    assert np.array_equal(np.signbit(got), np.signbit(z["values"]))  # code 8 is -0.0
+
+
+@pytest.mark.parametrize("fmt,N,K,g", [("e2m1", 64, 256, 32), ("e2m1", 33, 4096, 32), ("e2m1", 7, 192, 64),
+                                        ("gf4", 48, 1024, 128), ("gf4", 5, 784, 0), ("gf4", 9, 300, 0),
+                                        ("gf4", 3, 100, 0), ("gf4", 17, 512, 64)])
+def test_dequant_bit_exact(fmt, N, K, g):
+    pw = jq.pack_weight(_weights(N, K, N + K), jq.QuantSpec(fmt, g, 0))
+    got = ops.dequantize(pw.to(DEV)).cpu().numpy()
+    assert np.array_equal(got, _oracle_dequant(pw))
+
+
+def test_dequant_golden(golden_dir):
+    z = np.load(os.path.join(golden_dir, "e2m1_g32.npz"))
+    pw = jq.PackedWeight(jq.QuantSpec("e2m1", 32, 0), 64, 256, torch.from_numpy(z["qweight"]),
+                         torch.from_numpy(z["scales"]), None).to(DEV)
+    assert np.array_equal(ops.dequantize(pw).cpu().numpy(), z["w_hat"])
+    z = np.load(os.path.join(golden_dir, "gf4_g128_had.npz"))
+    pw = jq.PackedWeight(jq.QuantSpec("gf4", 128, 128), 32, 512, torch.from_numpy(z["qweight"]),
+                         torch.from_numpy(z["scales"]), torch.from_numpy(z["codebook"])).to(DEV)
+    assert np.array_equal(ops.dequantize(pw).cpu().numpy(), z["w_hat"])
+
+
+# ------------------------------------------------------------------- fwht ----
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_fwht_bit_exact(dtype, golden_dir):
+    g = torch.Generator("cpu").manual_seed(3)
+    x = (torch.randn(5, 1024, generator=g) * 3).to(dtype)
+    got = ops.fwht_block(x.to(DEV)).cpu().numpy()
+    assert np.array_equal(got, formats.fwht_block(x.float().numpy(), 128))
+    rows = np.load(os.path.join(golden_dir, "kat_fwht128.npz"))["rows"]
+    assert np.array_equal(ops.fwht_block(torch.eye(128, device=DEV)).cpu().numpy(), rows)
+
+
+# ------------------------------------------------------------------- gemv ----
+@pytest.mark.parametrize("B", [1, 2, 3, 4, 5, 8])
+@pytest.mark.parametrize("fmt,g,had", [("e2m1", 32, 0), ("gf4", 128, 128), ("gf4", 128, 0), ("e2m1", 64, 128)])
+def test_gemv_parity_batches(fmt, g, had, B):
+    pw = jq.pack_weight(_weights(203, 1024, 17), jq.QuantSpec(fmt, g, had))
+    gen = torch.Generator("cpu").manual_seed(B)
+    x = torch.randn(B, 1024, generator=gen).bfloat16()
+    _check_gemv(pw, x)
+
+
+@pytest.mark.parametrize("N,K,fmt,g,had", [(1, 128, "e2m1", 32, 128), (2, 32, "e2m1", 32, 0), (5, 64, "gf4", 0, 0),
+                                            (300, 784, "gf4", 0, 0), (100, 300, "gf4", 0, 0), (10, 100, "gf4", 0, 0),
+                                            (67, 2048 + 128, "gf4", 128, 128), (129, 11008, "gf4", 128, 128),
+                                            (64, 28672, "e2m1", 32, 0), (4099, 256, "e2m1", 32, 0)])
+def test_gemv_parity_shapes(N, K, fmt, g, had):
+    pw = jq.pack_weight(_weights(N, K, N * 7 + K), jq.QuantSpec(fmt, g, had))
+    gen = torch.Generator("cpu").manual_seed(N)
+    _check_gemv(pw, torch.rand(1, K, generator=gen), torch.randn(N, generator=gen))
+    _check_gemv(pw, torch.randn(2, K, generator=gen).half())
+
+
+def test_gemv_heavy_tailed_activations_and_extreme_magnitudes():
+    K = 4096
+    pw = jq.pack_weight(_weights(256, K, 2), jq.QuantSpec("gf4", 128, 128))
+    g = torch.Generator("cpu").manual_seed(2)
+    z = torch.randn(5, 1, K, generator=g)
+    x = z[0] / torch.sqrt((z[1:] ** 2).mean(dim=0))
+    x[:, torch.randperm(K, generator=g)[:8]] *= 50
+    _check_gemv(pw, x.bfloat16())
+    for scale in (1e-20, 1e-6, 1e8, 1e25):
+        _check_gemv(pw, (x * scale).float())
+    y0 = ops.linear(torch.zeros(1, K, device=DEV), pw.to(DEV))
+    assert torch.count_nonzero(y0) == 0
+
+
+def test_gemv_unit_vectors_read_back_dequantized_columns():
+    """x = e_k is exact in fp16, so y must equal column k of W_hat bit for bit."""
+    pw = jq.pack_weight(_weights(512, 1024, 4), jq.QuantSpec("e2m1", 32, 0)).to(DEV)
+    w_hat = ops.dequantize(pw)
+    for k in (0, 1, 31, 32, 517, 1023):
+        x = torch.zeros(1, 1024, device=DEV)
+        x[0, k] = 1.0
+        assert torch.equal(ops.linear(x, pw)[0], w_hat[:, k])
+
+
+def test_output_dtypes_round_once():
+    pw = jq.pack_weight(_weights(128, 512, 6), jq.QuantSpec("e2m1", 32, 0)).to(DEV)
+    x = torch.randn(3, 512, generator=torch.Generator("cpu").manual_seed(1)).bfloat16().to(DEV)
+    y32 = ops.linear(x, pw, out_dtype=torch.float32)
+    assert torch.equal(ops.linear(x, pw), y32.bfloat16())
+    assert torch.equal(ops.linear(x.half(), pw), ops.linear(x.half(), pw, out_dtype=torch.float32).half())
+
+
+def test_golden_vectors_through_the_kernel(golden_dir):
+    z = np.load(os.path.join(golden_dir, "e2m1_g32.npz"))
+    pw = jq.PackedWeight(jq.QuantSpec("e2m1", 32, 0), 64, 256, torch.from_numpy(z["qweight"]),
+                         torch.from_numpy(z["scales"]), None).to(DEV)
+    y = ops.linear(torch.from_numpy(z["x"]).bfloat16().to(DEV), pw, torch.from_numpy(z["bias"]).to(DEV),
+                   out_dtype=torch.float32)
+    assert formats.rel_err(y.cpu().numpy(), z["y"]) <= TOL
+    z = np.load(os.path.join(golden_dir, "gf4_g128_had.npz"))
+    pw = jq.PackedWeight(jq.QuantSpec("gf4", 128, 128), 32, 512, torch.from_numpy(z["qweight"]),
+                         torch.from_numpy(z["scales"]), torch.from_numpy(z["codebook"])).to(DEV)
+    y = ops.linear(torch.from_numpy(z["x"]).bfloat16().to(DEV), pw, out_dtype=torch.float32)
+    assert formats.rel_err(y.cpu().numpy(), z["y"]) <= TOL
+    z = np.load(os.path.join(golden_dir, "lenet300_pruned_rows.npz"))
+    pw = jq.PackedWeight(jq.QuantSpec("gf4", 0, 0), 24, 784, torch.from_numpy(z["qweight"]), None,
+                         torch.from_numpy(z["codebook"])).to(DEV)
+    y = ops.linear(torch.from_numpy(z["x"]).to(DEV), pw)
+    assert formats.rel_err(y.cpu().numpy(), z["y"]) <= TOL
+
+
+def test_mlp_784_300_100_10_matches_golden(golden_dir):
+    """The reference's model container (Flatten, Linear, ReLU, Linear, ReLU,
+    Linear) with every Linear swapped by quantize_module."""
+    z = np.load(os.path.join(golden_dir, "mlp_gf4.npz"))
+    g = torch.Generator("cpu").manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(784, 300, bias=False), torch.nn.ReLU(),
+                                torch.nn.Linear(300, 100, bias=False), torch.nn.ReLU(),
+                                torch.nn.Linear(100, 10, bias=False))
+    with torch.no_grad():
+        for idx, (n, k) in zip((1, 3, 5), [(300, 784), (100, 300), (10, 100)]):
+            model[idx].weight.copy_(torch.randn(n, k, generator=g) * k ** -0.5)
+    qm = jq.quantize_module(model, 4, fmt="gf4", group_size=0).to(DEV)
+    x = torch.from_numpy(z["x"]).to(DEV)
+    y = qm(x)
+    assert formats.rel_err(y.cpu().numpy(), z["y2"]) <= TOL
+    h = qm[1](x)
+    assert formats.rel_err(h.cpu().numpy(), z["y0"]) <= TOL
+    # commit() drops the dense weight; .weight stays readable as W_hat
+    qm[1].commit()
+    assert qm[1].hard_quant and torch.equal(qm[1](x), h)
+    assert qm[1].weight.shape == (300, 784) and qm[1].weight.dtype == torch.float32
+
+
+def test_leading_dims_and_large_batch_split():
+    pw = jq.pack_weight(_weights(96, 256, 8), jq.QuantSpec("e2m1", 32, 0)).to(DEV)
+    x = torch.randn(3, 7, 256, generator=torch.Generator("cpu").manual_seed(0)).to(DEV)
+    y = ops.linear(x, pw)
+    assert y.shape == (3, 7, 96)
+    y1 = torch.cat([ops.linear(x.reshape(21, 256)[i:i + 1], pw) for i in range(21)])
+    assert formats.rel_err(y.reshape(21, 96).cpu().numpy(), y1.cpu().numpy()) < 1e-6
+
+
+# ---------------------------------------------------------------- grouped ----
+@pytest.mark.parametrize("fmt,g,had,B", [("gf4", 128, 128, 1), ("e2m1", 32, 0, 2), ("gf4", 128, 128, 4)])
+def test_grouped_launch_equals_single_launches(fmt, g, had, B):
+    shapes = [(512, 1024), (96, 2048), (1000, 256), (3, 4096), (777, 1024)]
+    pws = [jq.pack_weight(_weights(n, k, n + k), jq.QuantSpec(fmt, g, had)).to(DEV) for n, k in shapes]
+    grp = ops.GroupedGemv(pws, B, torch.bfloat16)
+    gen = torch.Generator("cpu").manual_seed(9)
+    for x in grp.xs:
+        x.copy_(torch.randn(x.shape, generator=gen).bfloat16())
+    for y in grp.ys:
+        y.fill_(float("nan"))
+    grp.run()
+    torch.cuda.synchronize()
+    for pw, x, y in zip(pws, grp.xs, grp.ys):
+        assert torch.equal(y, ops.linear(x, pw))
+
+
+# ------------------------------------------------- full-size property tests ----
+def test_full_size_4096_e2m1_and_row_permutation():
+    g = torch.Generator("cpu").manual_seed(1)
+    W = (torch.randn(4096, 4096, generator=g) * 0.02).bfloat16().float()
+    pw = jq.pack_weight(W, jq.QuantSpec("e2m1", 32, 0))
+    x = torch.randn(1, 4096, generator=g).bfloat16()
+    _check_gemv(pw, x)
+    perm = torch.randperm(4096, generator=g)
+    pwp = jq.PackedWeight(pw.spec, pw.N, pw.K, pw.qweight[perm], pw.scales[perm], None).to(DEV)
+    y = ops.linear(x.to(DEV), pw.to(DEV), out_dtype=torch.float32)
+    yp = ops.linear(x.to(DEV), pwp, out_dtype=torch.float32)
+    assert torch.equal(yp[0], y[0][perm.to(DEV)])  # rows are independent: bit-exact
+
+
+def test_full_size_11008_gf4_hadamard():
+    g = torch.Generator("cpu").manual_seed(2)
+    W = torch.randn(11008, 4096, generator=g) * 0.02
+    W[torch.rand(11008, 4096, generator=g) < 0.001] *= 10
+    pw = jq.pack_weight(W, jq.QuantSpec("gf4", 128, 128))
+    z = torch.randn(5, 1, 4096, generator=g)
+    x = z[0] / torch.sqrt((z[1:] ** 2).mean(dim=0))
+    x[:, torch.randperm(4096, generator=g)[:8]] *= 50
+    _check_gemv(pw, x.bfloat16())
+    got = ops.dequantize(pw.to(DEV)).cpu().numpy()
+    assert np.array_equal(got, _oracle_dequant(pw))

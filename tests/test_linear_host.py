@@ -1,0 +1,65 @@
+"""Host-side mirror of the reference's QuantLinear / quantize_module surface
+(no GPU: nothing here launches a kernel)."""
+import inspect
+
+import pytest
+import torch
+import torch.nn as nn
+
+import if_i_could_turn_back_time_b200 as jq
+
+
+def test_constructor_signature_matches_reference():
+    params = list(inspect.signature(jq.JenksQuantLinear.__init__).parameters.values())
+    assert [p.name for p in params[:4]] == ["self", "linear_module", "bitwidth", "mask"]
+    assert params[2].default == 4 and params[3].default is None
+    assert all(p.kind is inspect.Parameter.KEYWORD_ONLY for p in params[4:])
+
+
+def test_attributes_and_commit():
+    lin = nn.Linear(256, 24)
+    q = jq.JenksQuantLinear(lin, 4, fmt="e2m1", group_size=32)
+    assert isinstance(q, nn.Linear) and q.in_features == 256 and q.out_features == 24
+    assert q.hard_quant is False and not q.weight.requires_grad
+    assert torch.equal(q.weight.data, lin.weight.data) and torch.equal(q.bias.data, lin.bias.data)
+    assert torch.equal(q.mask, torch.ones_like(lin.weight))
+    q.commit()
+    assert q.hard_quant is True and q._parameters["weight"] is None
+    sd = q.state_dict()
+    assert {"qweight", "scales", "bias", "mask"} <= set(sd) and "weight" not in sd
+    assert sd["qweight"].dtype == torch.uint8 and sd["qweight"].shape == (24, 128)
+
+
+def test_bitwidth_other_than_4_is_rejected():
+    with pytest.raises(ValueError):
+        jq.JenksQuantLinear(nn.Linear(64, 8), 8)
+
+
+def test_quantize_module_swaps_linears_and_keeps_sparsity_mask():
+    model = nn.Sequential(nn.Flatten(), nn.Linear(784, 300), nn.ReLU(), nn.Linear(300, 100), nn.ReLU(),
+                          nn.Linear(100, 10))
+    with torch.no_grad():
+        model[1].weight[:, ::2] = 0
+    qm = jq.quantize_module(model, 4, fmt="gf4", group_size=0)
+    assert isinstance(qm[1], jq.JenksQuantLinear) and isinstance(qm[3], jq.JenksQuantLinear)
+    assert isinstance(model[1], nn.Linear) and not isinstance(model[1], jq.JenksQuantLinear)  # deep copy
+    assert torch.equal(qm[1].mask, (model[1].weight != 0).float())
+    leaf = jq.quantize_module(nn.Linear(128, 4), 4, fmt="e2m1", group_size=32)
+    assert isinstance(leaf, jq.JenksQuantLinear)
+
+
+def test_forward_without_cuda_fails_loudly():
+    q = jq.JenksQuantLinear(nn.Linear(64, 8), 4, fmt="e2m1", group_size=32)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        q(torch.randn(2, 64))
+
+
+def test_spec_validation():
+    with pytest.raises(ValueError):
+        jq.QuantSpec("e2m1", 0, 0)
+    with pytest.raises(ValueError):
+        jq.QuantSpec("gf4", 48, 0)
+    with pytest.raises(ValueError):
+        jq.QuantSpec("gf4", 128, 64)
+    assert jq.algorithmic_bytes(jq.QuantSpec("e2m1", 32, 0), 4096, 4096, 1, 2, 2) == 9453568
+    assert jq.algorithmic_bytes(jq.QuantSpec("gf4", 128, 128), 11008, 4096, 1, 2, 2) == 23631360
