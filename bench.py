@@ -181,8 +181,8 @@ def cpu_reference_leg(name: str, batch: int, budget_s: float, steps: int = 1, wa
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode7b", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=1)

@@ -22,7 +22,10 @@ struct GemvProblem {
     int N, K, g, had;
 };
 
-constexpr int kThreads = 512;
+#ifndef JQ_THREADS
+#define JQ_THREADS 512
+#endif
+constexpr int kThreads = JQ_THREADS;
 constexpr int kWarps = kThreads / 32;
 
 template <int B>
@@ -96,137 +99,323 @@ __device__ void stage_activation(const GemvProblem &p, int x_dtype, __half *xs, 
     __syncthreads();
 }
 
-// One warp, R rows starting at row0, full K.  tab: R*16 halves of per-warp
-// shared memory (GF4 tables).
-template <int FMT, int B, int R>
-__device__ __forceinline__ void warp_rows(const GemvProblem &p, int row0, const __half *xs, const int *sexp,
-                                          __half *tab, int y_dtype) {
-    const int lane = threadIdx.x & 31;
-    const int K = p.K, N = p.N, XS = xs_halves(K);
-    const int stride_b = jq_row_stride_codes(K) >> 1;  // bytes per packed row
-    const int nchunks = jq_row_stride_codes(K) >> 5;
-    const int ngroups = p.g ? K / p.g : 0;
-    float acc[R][B];
+// ---- asynchronous per-thread prefetch ring ------------------------------------
+// Every thread copies exactly the 16-byte weight chunks (and the 4-byte scale
+// pairs) it will consume itself, with cp.async, DEPTH stages ahead, into
+// shared-memory slots only it reads.  No barrier of any kind guards the ring:
+// cp.async.wait_group orders a thread's own copies before its own loads.
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint16_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+// Eight E2M1 codes (one 32-bit word) times eight fp16 activations (x: four
+// half2), accumulated into two fp32 partial sums.  One asm block so that the
+// byte and half-word unpacking stays register sub-addressing instead of
+// shift/mask instructions: 4 cvt + 8 fma per word.
+__device__ __forceinline__ void dot8_e2m1(uint32_t word, const uint4 &x, float &p0, float &p1) {
+    asm("{ .reg .b8 b0, b1, b2, b3; .reg .b32 h0, h1, h2, h3;\n"
+        "  .reg .b16 wl0, wh0, wl1, wh1, wl2, wh2, wl3, wh3, xl0, xh0, xl1, xh1, xl2, xh2, xl3, xh3;\n"
+        "  mov.b32 {b0, b1, b2, b3}, %2;\n"
+        "  cvt.rn.f16x2.e2m1x2 h0, b0; cvt.rn.f16x2.e2m1x2 h1, b1;\n"
+        "  cvt.rn.f16x2.e2m1x2 h2, b2; cvt.rn.f16x2.e2m1x2 h3, b3;\n"
+        "  mov.b32 {wl0, wh0}, h0; mov.b32 {wl1, wh1}, h1; mov.b32 {wl2, wh2}, h2; mov.b32 {wl3, wh3}, h3;\n"
+        "  mov.b32 {xl0, xh0}, %3; mov.b32 {xl1, xh1}, %4; mov.b32 {xl2, xh2}, %5; mov.b32 {xl3, xh3}, %6;\n"
+        "  fma.rn.f32.f16 %0, wl0, xl0, %0; fma.rn.f32.f16 %1, wh0, xh0, %1;\n"
+        "  fma.rn.f32.f16 %0, wl1, xl1, %0; fma.rn.f32.f16 %1, wh1, xh1, %1;\n"
+        "  fma.rn.f32.f16 %0, wl2, xl2, %0; fma.rn.f32.f16 %1, wh2, xh2, %1;\n"
+        "  fma.rn.f32.f16 %0, wl3, xl3, %0; fma.rn.f32.f16 %1, wh3, xh3, %1; }"
+        : "+f"(p0), "+f"(p1)
+        : "r"(word), "r"(x.x), "r"(x.y), "r"(x.z), "r"(x.w));
+}
+
+// Same for B > 1: the four converted half2 are produced once and reused.
+__device__ __forceinline__ void cvt8_e2m1(uint32_t word, uint32_t (&h)[4]) {
+    asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %4;\n"
+        "  cvt.rn.f16x2.e2m1x2 %0, b0; cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "  cvt.rn.f16x2.e2m1x2 %2, b2; cvt.rn.f16x2.e2m1x2 %3, b3; }"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+        : "r"(word));
+}
+__device__ __forceinline__ void dot8_h2(const uint32_t (&h)[4], const uint4 &x, float &p0, float &p1) {
+    asm("{ .reg .b16 wl0, wh0, wl1, wh1, wl2, wh2, wl3, wh3, xl0, xh0, xl1, xh1, xl2, xh2, xl3, xh3;\n"
+        "  mov.b32 {wl0, wh0}, %2; mov.b32 {wl1, wh1}, %3; mov.b32 {wl2, wh2}, %4; mov.b32 {wl3, wh3}, %5;\n"
+        "  mov.b32 {xl0, xh0}, %6; mov.b32 {xl1, xh1}, %7; mov.b32 {xl2, xh2}, %8; mov.b32 {xl3, xh3}, %9;\n"
+        "  fma.rn.f32.f16 %0, wl0, xl0, %0; fma.rn.f32.f16 %1, wh0, xh0, %1;\n"
+        "  fma.rn.f32.f16 %0, wl1, xl1, %0; fma.rn.f32.f16 %1, wh1, xh1, %1;\n"
+        "  fma.rn.f32.f16 %0, wl2, xl2, %0; fma.rn.f32.f16 %1, wh2, xh2, %1;\n"
+        "  fma.rn.f32.f16 %0, wl3, xl3, %0; fma.rn.f32.f16 %1, wh3, xh3, %1; }"
+        : "+f"(p0), "+f"(p1)
+        : "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]), "r"(x.x), "r"(x.y), "r"(x.z), "r"(x.w));
+}
+
+// Eight GF4 codes: each nibble, doubled, is OR-ed into the 32-byte-aligned
+// shared address of the row's 16-entry fp16 table (shift + one LOP3), looked up
+// with a 16-bit shared load and packed pairwise into half2.
+__device__ __forceinline__ void lut8_gf4(uint32_t word, uint32_t tb, uint32_t (&h)[4]) {
 #pragma unroll
-    for (int r = 0; r < R; ++r)
+    for (int bb = 0; bb < 4; ++bb) {
+        const uint32_t s0 = bb == 0 ? (word << 1) : (word >> (8 * bb - 1));
+        const uint32_t s1 = word >> (8 * bb + 3);
+        uint32_t o0, o1;
+        asm("lop3.b32 %0, %1, 0x1e, %2, 0xea;" : "=r"(o0) : "r"(s0), "r"(tb));  // (a & b) | c
+        asm("lop3.b32 %0, %1, 0x1e, %2, 0xea;" : "=r"(o1) : "r"(s1), "r"(tb));
+        asm("{ .reg .b16 lo, hi; ld.shared.u16 lo, [%1]; ld.shared.u16 hi, [%2]; mov.b32 %0, {lo, hi}; }"
+            : "=r"(h[bb])
+            : "r"(o0), "r"(o1));
+    }
+}
+
+template <int B, int DEPTH>
+struct Ring {
+    static constexpr int T = Tile<B>::R;                       // rows per stage
+    static constexpr int kSlots = DEPTH * T;                   // 16-byte slots per thread
+    static constexpr int kWBytes = kSlots * kThreads * 16;     // weight ring
+    static constexpr int kSBytes = kSlots * kThreads * 4;      // scale-pair ring
+    static constexpr int kTabBytes = kWarps * DEPTH * T * 32 + 32;  // GF4 codebooks per warp and row group (+ alignment slack)
+    static constexpr int kBytes = kWBytes + kSBytes + kTabBytes;
+};
+
+// All row groups [rg_lo, rg_hi) of one problem, by one CTA.  Warp w takes the
+// row groups rg_lo + w, rg_lo + w + kWarps, ...; a row group is T adjacent rows.
+// Everything that is constant over a row group (row pointers, scale-pair
+// parity) is computed once per row group, so that a stage costs little beyond
+// its copies, its shared loads and the dot products themselves.
+template <int FMT, int B, int DEPTH>
+__device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __half *xs, const int *sexp,
+                         unsigned char *ring_base, int y_dtype) {
+    using R_ = Ring<B, DEPTH>;
+    constexpr int T = R_::T;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = p.K, N = p.N, XS = xs_halves(K);
+    const int stride_b = jq_row_stride_codes(K) >> 1;
+    const int nchunks = jq_row_stride_codes(K) >> 5;
+    const int nit = (nchunks + 31) >> 5;
+    const int ngroups = p.g ? K / p.g : 0;
+    const int gq = p.g >> 5;                             // chunks per scale group
+    const bool gpow2 = p.g && (gq & (gq - 1)) == 0;
+    const int gshift = p.g ? (31 - __clz(gq)) : 0;
+    // Fast scale path: 4-byte cp.async of the aligned fp16 pair holding this
+    // lane's scale.  Needs a power-of-two group of at most 512 codes (so the
+    // pair pointer advances by a constant, 4-byte-multiple step per stage), an
+    // even element count (the pair never crosses the end) and an aligned base.
+    const bool scale_async = p.g && gpow2 && p.g <= 512 && (((size_t)N * ngroups) & 1) == 0 &&
+                             (reinterpret_cast<uintptr_t>(p.scales) & 3u) == 0;
+    const int sadv = scale_async ? (2048 / p.g) : 0;     // bytes the pair pointer moves per stage (32 chunks)
+    const int g_lane = p.g ? (gpow2 ? (lane >> gshift) : (lane * 32) / p.g) : 0;  // group of chunk `lane`
+
+    const uint32_t wring = smem_u32(ring_base) + tid * 16;
+    const uint32_t sring = smem_u32(ring_base + R_::kWBytes) + tid * 4;
+    const uint32_t tabs = ((smem_u32(ring_base + R_::kWBytes + R_::kSBytes) + 31u) & ~31u) + warp * (DEPTH * T * 32);
+    const uint32_t xs_u = smem_u32(xs) + lane * 16;
+
+    const int first = rg_lo + warp;
+    const int nrg = first < rg_hi ? (rg_hi - first + kWarps - 1) / kWarps : 0;
+    const int total = nrg * nit;
+
+    // ---- producer state ----
+    int is = 0, ii = 0, irg = first, islot = 0, itab = 0;
+    const uint8_t *wptr[T];
+    const char *sptr[T];
+    auto issue = [&]() {
+        if (is < total) {
+            if (ii == 0) {
+#pragma unroll
+                for (int r = 0; r < T; ++r) {
+                    const int row = min(irg * T + r, N - 1);
+                    wptr[r] = p.qw + (size_t)row * stride_b + lane * 16;
+                    if (scale_async)
+                        sptr[r] = reinterpret_cast<const char *>(p.scales) + (((size_t)row * ngroups + g_lane) & ~(size_t)1) * 2;
+                }
+                if (FMT == JQ_FMT_GF4) {
+                    __syncwarp();  // nobody still reads the table buffer being replaced
+                    if (lane < T * 2) {
+                        const int row = min(irg * T + (lane >> 1), N - 1);
+                        cp_async16(tabs + itab * (T * 32) + lane * 16, p.codebook + (size_t)row * 16 + (lane & 1) * 8);
+                    }
+                }
+            }
+            if (lane + 32 * ii < nchunks) {
+#pragma unroll
+                for (int r = 0; r < T; ++r) {
+                    cp_async16(wring + (islot * T + r) * (kThreads * 16), wptr[r]);
+                    if (scale_async) cp_async4(sring + (islot * T + r) * (kThreads * 4), sptr[r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < T; ++r) {
+                wptr[r] += 512;
+                if (scale_async) sptr[r] += sadv;
+            }
+            if (++ii == nit) { ii = 0; irg += kWarps; itab = (itab + 1 == DEPTH) ? 0 : itab + 1; }
+        }
+        ++is;
+        islot = (islot + 1 == DEPTH) ? 0 : islot + 1;
+        cp_async_commit();
+    };
+
+#pragma unroll
+    for (int d = 0; d < DEPTH - 1; ++d) issue();
+
+    float acc[T][B];
+#pragma unroll
+    for (int r = 0; r < T; ++r)
 #pragma unroll
         for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
 
-    int rows[R];
+    // ---- consumer state ----
+    int ci = 0, crg = first, cslot = 0, ctab = 0;
+    uint32_t sel[T];  // byte-permute selectors picking this lane's fp16 out of the copied pair
+    for (int s = 0; s < total; ++s) {
+        issue();
+        cp_async_wait<DEPTH - 1>();
+        if (ci == 0) {
+            if (FMT == JQ_FMT_GF4) __syncwarp();  // the codebooks were copied by other lanes
+            if (scale_async) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) rows[r] = min(row0 + r, N - 1);
-
-    if (FMT == JQ_FMT_GF4) {
-        __syncwarp();
-        if (lane < R * 8) {
-            const int r = lane >> 3;
-            reinterpret_cast<uint32_t *>(tab)[lane] =
-                reinterpret_cast<const uint32_t *>(p.codebook + (size_t)rows[r] * 16)[lane & 7];
+                for (int r = 0; r < T; ++r) {
+                    const int row = min(crg * T + r, N - 1);
+                    sel[r] = ((row & ngroups & 1) ^ (g_lane & 1)) ? 0x4432u : 0x4410u;
+                }
+            }
         }
-        __syncwarp();
-    }
-
-    for (int c = lane; c < nchunks; c += 32) {
-        uint4 w[R];
-        float sc[R];
+        const int c = lane + 32 * ci;
+        if (c < nchunks) {
+            uint4 w[T];
+            float sc[T];
+            float part[T][B][2];
 #pragma unroll
-        for (int r = 0; r < R; ++r) w[r] = ldg_stream_u4(p.qw + (size_t)rows[r] * stride_b + (size_t)c * 16);
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            if (p.g) {
-                int gi = min((c * 32) / p.g, ngroups - 1);
-                sc[r] = __half2float(p.scales[(size_t)rows[r] * ngroups + gi]);
-            } else {
+            for (int r = 0; r < T; ++r) {
+                w[r] = lds128(wring + (cslot * T + r) * (kThreads * 16));
                 sc[r] = 1.f;
-            }
-        }
-        const int i = c >> 5;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            uint4 xv[B];
-#pragma unroll
-            for (int b = 0; b < B; ++b)
-                xv[b] = *reinterpret_cast<const uint4 *>(xs + (size_t)b * XS + (((i * 4 + q) * 32 + lane) << 3));
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const uint32_t word = q == 0 ? w[r].x : (q == 1 ? w[r].y : (q == 2 ? w[r].z : w[r].w));
-                float part[B];
-#pragma unroll
-                for (int b = 0; b < B; ++b) part[b] = 0.f;
-#pragma unroll
-                for (int bb = 0; bb < 4; ++bb) {
-                    uint16_t w0, w1;
-                    if (FMT == JQ_FMT_E2M1) {
-                        uint32_t h2 = e2m1x2_to_h2((word >> (8 * bb)) & 0xffu);
-                        w0 = h2_lo(h2);
-                        w1 = h2_hi(h2);
+                if (p.g) {
+                    uint32_t hb;
+                    if (scale_async) {
+                        hb = __byte_perm(lds32(sring + (cslot * T + r) * (kThreads * 4)), 0, sel[r]);
                     } else {
-                        const uint16_t *t = reinterpret_cast<const uint16_t *>(tab) + r * 16;
-                        w0 = t[(word >> (8 * bb)) & 0xfu];
-                        w1 = t[(word >> (8 * bb + 4)) & 0xfu];
+                        const int row = min(crg * T + r, N - 1);
+                        const int gi = gpow2 ? (c >> gshift) : (c * 32) / p.g;
+                        hb = reinterpret_cast<const uint16_t *>(p.scales)[(size_t)row * ngroups + gi];
                     }
-#pragma unroll
-                    for (int b = 0; b < B; ++b) {
-                        const uint32_t xx = bb == 0 ? xv[b].x : (bb == 1 ? xv[b].y : (bb == 2 ? xv[b].z : xv[b].w));
-                        fma_h(part[b], w0, h2_lo(xx));
-                        fma_h(part[b], w1, h2_hi(xx));
-                    }
+                    sc[r] = __half2float(__ushort_as_half((uint16_t)hb));
                 }
 #pragma unroll
-                for (int b = 0; b < B; ++b) acc[r][b] = fmaf(part[b], sc[r], acc[r][b]);
+                for (int b = 0; b < B; ++b) part[r][b][0] = part[r][b][1] = 0.f;
             }
-        }
-    }
 #pragma unroll
-    for (int r = 0; r < R; ++r)
+            for (int q = 0; q < 4; ++q) {
+                uint4 xv[B];  // the 8 activations of 16-byte piece q, per batch row
 #pragma unroll
-        for (int b = 0; b < B; ++b) acc[r][b] = warp_sum(acc[r][b]);
-    if (lane == 0) {
+                for (int b = 0; b < B; ++b) xv[b] = lds128(xs_u + (uint32_t)(b * XS + (((ci * 4 + q) * 32) << 3)) * 2);
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            if (row0 + r < N) {
-                const float bias = p.bias ? p.bias[row0 + r] : 0.f;
+                for (int r = 0; r < T; ++r) {
+                    const uint32_t word = q == 0 ? w[r].x : (q == 1 ? w[r].y : (q == 2 ? w[r].z : w[r].w));
+                    if (FMT == JQ_FMT_E2M1 && B == 1) {
+                        dot8_e2m1(word, xv[0], part[r][0][0], part[r][0][1]);
+                    } else {
+                        uint32_t h[4];
+                        if (FMT == JQ_FMT_E2M1) cvt8_e2m1(word, h);
+                        else lut8_gf4(word, tabs + ctab * (T * 32) + r * 32, h);
 #pragma unroll
-                for (int b = 0; b < B; ++b) {
-                    const float up = __uint_as_float((uint32_t)(127 + sexp[b]) << 23);  // 2^e
-                    store_out(p.y, (size_t)b * N + row0 + r, fmaf(acc[r][b], up, bias), y_dtype);
+                        for (int b = 0; b < B; ++b) dot8_h2(h, xv[b], part[r][b][0], part[r][b][1]);
+                    }
                 }
             }
+#pragma unroll
+            for (int r = 0; r < T; ++r)
+#pragma unroll
+                for (int b = 0; b < B; ++b) acc[r][b] = fmaf(part[r][b][0] + part[r][b][1], sc[r], acc[r][b]);
+        }
+        cslot = (cslot + 1 == DEPTH) ? 0 : cslot + 1;
+        if (++ci == nit) {
+#pragma unroll
+            for (int r = 0; r < T; ++r)
+#pragma unroll
+                for (int b = 0; b < B; ++b) acc[r][b] = warp_sum(acc[r][b]);
+            if (lane == 0) {
+#pragma unroll
+                for (int r = 0; r < T; ++r) {
+                    const int row = crg * T + r;
+                    if (row < N) {
+                        const float bias = p.bias ? p.bias[row] : 0.f;
+#pragma unroll
+                        for (int b = 0; b < B; ++b) {
+                            const float up = __uint_as_float((uint32_t)(127 + sexp[b]) << 23);  // 2^e
+                            store_out(p.y, (size_t)b * N + row, fmaf(acc[r][b], up, bias), y_dtype);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < T; ++r)
+#pragma unroll
+                for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
+            ci = 0;
+            crg += kWarps;
+            ctab = (ctab + 1 == DEPTH) ? 0 : ctab + 1;
         }
     }
+    cp_async_wait<0>();
 }
 
-template <int FMT, int B>
-__global__ void __launch_bounds__(kThreads) gemv_kernel(GemvProblem p, int x_dtype, int y_dtype) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int R = Tile<B>::R;
-    const int XS = xs_halves(p.K);
-    __half *xs = reinterpret_cast<__half *>(smem);
-    __half *tabs = xs + (size_t)B * XS;                     // kWarps * R * 16 halves
-    float *sred = reinterpret_cast<float *>(tabs + kWarps * R * 16);
-    int *sexp = reinterpret_cast<int *>(sred + kWarps);
+struct SmemLayout {
+    __half *xs;
+    float *sred;
+    int *sexp;
+    unsigned char *ring;
+};
 
-    stage_activation<B>(p, x_dtype, xs, sred, sexp);
-
-    const int warp = threadIdx.x >> 5;
-    const int total_warps = gridDim.x * kWarps;
-    const int ngroups_rows = (p.N + R - 1) / R;
-    for (int rg = blockIdx.x * kWarps + warp; rg < ngroups_rows; rg += total_warps)
-        warp_rows<FMT, B, R>(p, rg * R, xs, sexp, tabs + warp * R * 16, y_dtype);
+template <int B, int DEPTH>
+__device__ __forceinline__ SmemLayout carve(unsigned char *smem, int maxK) {
+    SmemLayout L;
+    L.ring = smem;  // 16-byte aligned slots first
+    L.xs = reinterpret_cast<__half *>(smem + Ring<B, DEPTH>::kBytes);
+    L.sred = reinterpret_cast<float *>(L.xs + (size_t)B * xs_halves(maxK));
+    L.sexp = reinterpret_cast<int *>(L.sred + kWarps);
+    return L;
 }
 
-// Grouped launch: the concatenated row space of all problems is split into
-// contiguous, byte-balanced CTA ranges on the host (cta_first[]: first global
-// row-group of each CTA, in units of R rows); a CTA re-stages the activation
-// whenever it crosses into the next problem.
-template <int FMT, int B>
-__global__ void __launch_bounds__(kThreads) gemv_grouped_kernel(const jq_problem *probs, int nprob,
-                                                                  const int *rg_start, const int *cta_first,
-                                                                  int x_dtype, int y_dtype) {
+template <int FMT, int B, int DEPTH>
+__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvProblem p, int x_dtype, int y_dtype) {
     extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int R = Tile<B>::R;
+    const SmemLayout L = carve<B, DEPTH>(smem, p.K);
+    stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp);
+    constexpr int T = Tile<B>::R;
+    const long long nrg = (p.N + T - 1) / T;
+    const int lo = (int)(nrg * blockIdx.x / gridDim.x), hi = (int)(nrg * (blockIdx.x + 1) / gridDim.x);
+    cta_rows<FMT, B, DEPTH>(p, lo, hi, L.xs, L.sexp, L.ring, y_dtype);
+}
+
+// Grouped launch: the concatenated row-group space of all problems is split
+// into contiguous, byte-balanced CTA ranges on the host (cta_first[]); a CTA
+// re-stages the activation whenever it crosses into the next problem.
+template <int FMT, int B, int DEPTH>
+__global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_problem *probs, int nprob,
+                                                                     const int *rg_start, const int *cta_first,
+                                                                     int maxK, int x_dtype, int y_dtype) {
+    extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int s_prob;
-    const int warp = threadIdx.x >> 5;
+    const SmemLayout L = carve<B, DEPTH>(smem, maxK);
     int rg = cta_first[blockIdx.x];
     const int rg_end = cta_first[blockIdx.x + 1];
     int pi = 0;
@@ -245,24 +434,18 @@ __global__ void __launch_bounds__(kThreads) gemv_grouped_kernel(const jq_problem
         p.codebook = reinterpret_cast<const __half *>(jp.codebook);
         p.x = jp.x; p.bias = jp.bias; p.y = jp.y;
         p.N = jp.N; p.K = jp.K; p.g = jp.g; p.had = jp.had_block;
-        const int XS = xs_halves(p.K);
-        __half *xs = reinterpret_cast<__half *>(smem);
-        __half *tabs = xs + (size_t)B * XS;
-        float *sred = reinterpret_cast<float *>(tabs + kWarps * R * 16);
-        int *sexp = reinterpret_cast<int *>(sred + kWarps);
-        stage_activation<B>(p, x_dtype, xs, sred, sexp);
+        stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp);
         const int base = rg_start[pi];
         const int lim = min(rg_end, rg_start[pi + 1]);
-        for (int t = rg + warp; t < lim; t += kWarps)
-            warp_rows<FMT, B, R>(p, (t - base) * R, xs, sexp, tabs + warp * R * 16, y_dtype);
+        cta_rows<FMT, B, DEPTH>(p, rg - base, lim - base, L.xs, L.sexp, L.ring, y_dtype);
         rg = lim;
         __syncthreads();  // all warps done with xs before the next problem restages it
     }
 }
 
-template <int B>
+template <int B, int DEPTH>
 static size_t gemv_smem_bytes(int K) {
-    return (size_t)B * xs_halves(K) * 2 + (size_t)kWarps * Tile<B>::R * 16 * 2 + kWarps * 4 + 8 * 4;
+    return (size_t)Ring<B, DEPTH>::kBytes + (size_t)B * xs_halves(K) * 2 + kWarps * 4 + 8 * 4;
 }
 
 }  // namespace jq
@@ -289,24 +472,63 @@ static bool dtype_ok(int d) { return d == JQ_F32 || d == JQ_F16 || d == JQ_BF16;
 
 static const size_t kMaxSmem = 227 * 1024;
 
-template <int FMT, int B>
-static int launch_gemv(const GemvProblem &p, int x_dtype, int y_dtype, cudaStream_t st) {
-    const size_t smem = gemv_smem_bytes<B>(p.K);
+template <int FMT, int B, int DEPTH>
+static int launch_gemv_d(const GemvProblem &p, int x_dtype, int y_dtype, cudaStream_t st) {
+    const size_t smem = gemv_smem_bytes<B, DEPTH>(p.K);
     if (smem > kMaxSmem) return JQ_ERR_UNSUPPORTED;
-    auto kern = gemv_kernel<FMT, B>;
+    auto kern = gemv_kernel<FMT, B, DEPTH>;
     JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const int sms = jq_sm_count();
-    const int per_sm = smem * 2 + 2048 <= kMaxSmem ? 2 : 1;
     const int row_groups = (p.N + Tile<B>::R - 1) / Tile<B>::R;
-    int grid = sms * per_sm;
+    int grid = jq_sm_count();  // one persistent CTA per SM
     const int need = (row_groups + kWarps - 1) / kWarps;
     if (grid > need) grid = need;
     kern<<<grid, kThreads, smem, st>>>(p, x_dtype, y_dtype);
     return jq_launch_status();
 }
 
+// deepest prefetch ring that fits beside the staged activation
+template <int FMT, int B>
+static int launch_gemv(const GemvProblem &p, int x_dtype, int y_dtype, cudaStream_t st) {
+    if (gemv_smem_bytes<B, 4>(p.K) <= kMaxSmem) return launch_gemv_d<FMT, B, 4>(p, x_dtype, y_dtype, st);
+    return launch_gemv_d<FMT, B, 2>(p, x_dtype, y_dtype, st);
+}
+
+template <int B>
+static bool gemv_fits(int K) { return gemv_smem_bytes<B, 2>(K) <= kMaxSmem; }
+
+static bool gemv_fits_b(int B, int K) {
+    switch (B) {
+        case 1: return gemv_fits<1>(K); case 2: return gemv_fits<2>(K); case 3: return gemv_fits<3>(K);
+        case 4: return gemv_fits<4>(K); case 5: return gemv_fits<5>(K); case 6: return gemv_fits<6>(K);
+        case 7: return gemv_fits<7>(K); case 8: return gemv_fits<8>(K); default: return false;
+    }
+}
+
+template <int FMT>
+static int dispatch_gemv_one(const GemvProblem &p, int B, int x_dtype, int y_dtype, cudaStream_t st);
+
+// Batches whose staged activation does not fit in shared memory are run as
+// several launches over sub-batches.
 template <int FMT>
 static int dispatch_gemv(const GemvProblem &p, int B, int x_dtype, int y_dtype, cudaStream_t st) {
+    if (B > 8) return JQ_ERR_UNSUPPORTED;
+    int bc = B;
+    while (bc > 1 && !gemv_fits_b(bc, p.K)) --bc;
+    if (!gemv_fits_b(bc, p.K)) return JQ_ERR_UNSUPPORTED;
+    const size_t xe = x_dtype == JQ_F32 ? 4 : 2, ye = y_dtype == JQ_F32 ? 4 : 2;
+    for (int b0 = 0; b0 < B; b0 += bc) {
+        GemvProblem q = p;
+        const int nb = B - b0 < bc ? B - b0 : bc;
+        q.x = reinterpret_cast<const char *>(p.x) + (size_t)b0 * p.K * xe;
+        q.y = reinterpret_cast<char *>(p.y) + (size_t)b0 * p.N * ye;
+        int st_ = dispatch_gemv_one<FMT>(q, nb, x_dtype, y_dtype, st);
+        if (st_) return st_;
+    }
+    return JQ_OK;
+}
+
+template <int FMT>
+static int dispatch_gemv_one(const GemvProblem &p, int B, int x_dtype, int y_dtype, cudaStream_t st) {
     switch (B) {
         case 1: return launch_gemv<FMT, 1>(p, x_dtype, y_dtype, st);
         case 2: return launch_gemv<FMT, 2>(p, x_dtype, y_dtype, st);
@@ -353,7 +575,7 @@ static const int kPlanHeader = 8;
 
 extern "C" size_t jq_grouped_plan_bytes(int n) {
     if (n < 0) return 0;
-    return ((size_t)kPlanHeader + (size_t)(n + 1) + (size_t)jq_sm_count() * 2 + 1) * sizeof(int);
+    return ((size_t)kPlanHeader + (size_t)(n + 1) + (size_t)jq_sm_count() + 1) * sizeof(int);
 }
 
 template <int B>
@@ -374,7 +596,7 @@ extern "C" int jq_grouped_plan(int fmt, const jq_problem *ph, int n, int B, void
     const int R = tile_rows(B);
     if (!R) return JQ_ERR_UNSUPPORTED;
     if (plan_bytes < jq_grouped_plan_bytes(n)) return JQ_ERR_WORKSPACE;
-    const int grid = jq_sm_count() * 2;
+    const int grid = jq_sm_count();  // one persistent CTA per SM
     int *h = reinterpret_cast<int *>(plan_host);
     int *rg_start = h + kPlanHeader, *cta_first = rg_start + n + 1;
     int maxK = 0;
@@ -421,16 +643,24 @@ extern "C" int jq_grouped_plan(int fmt, const jq_problem *ph, int n, int B, void
     return JQ_OK;
 }
 
+template <int FMT, int B, int DEPTH>
+static int launch_grouped_d(const jq_problem *pd, const int *plan_host, const int *plan_dev, int x_dtype, int y_dtype,
+                            cudaStream_t st) {
+    const int n = plan_host[1], grid = plan_host[2], maxK = plan_host[3];
+    const size_t smem = gemv_smem_bytes<B, DEPTH>(maxK);
+    if (smem > kMaxSmem) return JQ_ERR_UNSUPPORTED;
+    auto kern = gemv_grouped_kernel<FMT, B, DEPTH>;
+    JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, kThreads, smem, st>>>(pd, n, plan_dev + kPlanHeader, plan_dev + kPlanHeader + n + 1, maxK, x_dtype, y_dtype);
+    return jq_launch_status();
+}
+
 template <int FMT, int B>
 static int launch_grouped(const jq_problem *pd, const int *plan_host, const int *plan_dev, int x_dtype, int y_dtype,
                           cudaStream_t st) {
-    const int n = plan_host[1], grid = plan_host[2], maxK = plan_host[3];
-    const size_t smem = gemv_smem_bytes<B>(maxK);
-    if (smem * 2 + 2048 > kMaxSmem) return JQ_ERR_UNSUPPORTED;
-    auto kern = gemv_grouped_kernel<FMT, B>;
-    JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kThreads, smem, st>>>(pd, n, plan_dev + kPlanHeader, plan_dev + kPlanHeader + n + 1, x_dtype, y_dtype);
-    return jq_launch_status();
+    if (gemv_smem_bytes<B, 4>(plan_host[3]) <= kMaxSmem)
+        return launch_grouped_d<FMT, B, 4>(pd, plan_host, plan_dev, x_dtype, y_dtype, st);
+    return launch_grouped_d<FMT, B, 2>(pd, plan_host, plan_dev, x_dtype, y_dtype, st);
 }
 
 template <int FMT>
