@@ -46,6 +46,7 @@ WORKLOADS = {
                                        ("down", 8192, 28672, 1)], 0.015),
     "e2m1_4096": ("e2m1", 32, 0, 16, [("linear", 4096, 4096, 1)], 0.02),
     "gf4_11008": ("gf4", 128, 128, 16, [("linear", 11008, 4096, 1)], 0.02),
+    "e2m1_8192": ("e2m1", 32, 0, 16, [("linear", 8192, 8192, 1)], 0.02),
 }
 
 
@@ -117,7 +118,7 @@ def build_stack(name: str, rank: int, world: int, batch: int, device, threads: i
     import if_i_could_turn_back_time_b200 as jq
     fmt, g, had, layers, mats, std = WORKLOADS[name]
     spec = jq.QuantSpec(fmt, g, had)
-    gen = torch.Generator("cpu").manual_seed({"decode7b": 3, "decode70b": 4, "e2m1_4096": 1, "gf4_11008": 2}[name])
+    gen = torch.Generator("cpu").manual_seed({"decode7b": 3, "decode70b": 4, "e2m1_4096": 1, "gf4_11008": 2, "e2m1_8192": 5}[name])
     proto = {}
     t0 = time.time()
     for label, N, K, _ in mats:

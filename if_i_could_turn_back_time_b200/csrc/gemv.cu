@@ -169,10 +169,12 @@ __device__ __forceinline__ void dot8_h2(const uint32_t (&h)[4], const uint4 &x, 
         : "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]), "r"(x.x), "r"(x.y), "r"(x.z), "r"(x.w));
 }
 
-// Eight GF4 codes: each nibble, doubled, is OR-ed into the 32-byte-aligned
-// shared address of the row's 16-entry fp16 table (shift + one LOP3), looked up
-// with a 16-bit shared load and packed pairwise into half2.
-__device__ __forceinline__ void lut8_gf4(uint32_t word, uint32_t tb, uint32_t (&h)[4]) {
+// Eight GF4 codes times B x eight activations.  Each nibble, doubled, is OR-ed
+// into the 32-byte-aligned shared address of the row's 16-entry fp16 table
+// (one shift + one LOP3), looked up with a 16-bit shared load, and fed to the
+// mixed-precision FMA as a 16-bit register (no repacking).
+template <int B>
+__device__ __forceinline__ void dot8_gf4(uint32_t word, uint32_t tb, const uint4 (&x)[B], float (&part)[B][2]) {
 #pragma unroll
     for (int bb = 0; bb < 4; ++bb) {
         const uint32_t s0 = bb == 0 ? (word << 1) : (word >> (8 * bb - 1));
@@ -180,9 +182,17 @@ __device__ __forceinline__ void lut8_gf4(uint32_t word, uint32_t tb, uint32_t (&
         uint32_t o0, o1;
         asm("lop3.b32 %0, %1, 0x1e, %2, 0xea;" : "=r"(o0) : "r"(s0), "r"(tb));  // (a & b) | c
         asm("lop3.b32 %0, %1, 0x1e, %2, 0xea;" : "=r"(o1) : "r"(s1), "r"(tb));
-        asm("{ .reg .b16 lo, hi; ld.shared.u16 lo, [%1]; ld.shared.u16 hi, [%2]; mov.b32 %0, {lo, hi}; }"
-            : "=r"(h[bb])
-            : "r"(o0), "r"(o1));
+        uint16_t w0, w1;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(w0) : "r"(o0));
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(w1) : "r"(o1));
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+            const uint32_t xx = bb == 0 ? x[b].x : (bb == 1 ? x[b].y : (bb == 2 ? x[b].z : x[b].w));
+            asm("{ .reg .b16 xl, xh; mov.b32 {xl, xh}, %4;\n"
+                "  fma.rn.f32.f16 %0, %2, xl, %0; fma.rn.f32.f16 %1, %3, xh, %1; }"
+                : "+f"(part[b][0]), "+f"(part[b][1])
+                : "h"(w0), "h"(w1), "r"(xx));
+        }
     }
 }
 
@@ -330,12 +340,13 @@ __device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __hal
 #pragma unroll
                 for (int r = 0; r < T; ++r) {
                     const uint32_t word = q == 0 ? w[r].x : (q == 1 ? w[r].y : (q == 2 ? w[r].z : w[r].w));
-                    if (FMT == JQ_FMT_E2M1 && B == 1) {
+                    if (FMT == JQ_FMT_GF4) {
+                        dot8_gf4<B>(word, tabs + ctab * (T * 32) + r * 32, xv, part[r]);
+                    } else if (B == 1) {
                         dot8_e2m1(word, xv[0], part[r][0][0], part[r][0][1]);
                     } else {
                         uint32_t h[4];
-                        if (FMT == JQ_FMT_E2M1) cvt8_e2m1(word, h);
-                        else lut8_gf4(word, tabs + ctab * (T * 32) + r * 32, h);
+                        cvt8_e2m1(word, h);
 #pragma unroll
                         for (int b = 0; b < B; ++b) dot8_h2(h, xv[b], part[r][b][0], part[r][b][1]);
                     }
