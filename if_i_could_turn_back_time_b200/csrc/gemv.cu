@@ -28,10 +28,16 @@ struct GemvProblem {
 constexpr int kThreads = JQ_THREADS;
 constexpr int kWarps = kThreads / 32;
 
-template <int B>
+#ifndef JQ_T_E2M1
+#define JQ_T_E2M1 4
+#endif
+#ifndef JQ_T_GF4
+#define JQ_T_GF4 4
+#endif
+template <int FMT, int B>
 struct Tile {
-    // rows a warp carries at once; bounded by registers
-    static constexpr int R = (B <= 2) ? 4 : (B <= 4 ? 2 : 1);
+    // rows a warp carries at once; bounded by registers and by the ring's shared memory
+    static constexpr int R = (B <= 2) ? (FMT == JQ_FMT_GF4 ? JQ_T_GF4 : JQ_T_E2M1) : (B <= 4 ? 2 : 1);
 };
 
 // halves of shared memory one batch row of the activation occupies
@@ -196,9 +202,9 @@ __device__ __forceinline__ void dot8_gf4(uint32_t word, uint32_t tb, const uint4
     }
 }
 
-template <int B, int DEPTH>
+template <int FMT, int B, int DEPTH>
 struct Ring {
-    static constexpr int T = Tile<B>::R;                       // rows per stage
+    static constexpr int T = Tile<FMT, B>::R;                       // rows per stage
     static constexpr int kSlots = DEPTH * T;                   // 16-byte slots per thread
     static constexpr int kWBytes = kSlots * kThreads * 16;     // weight ring
     static constexpr int kSBytes = kSlots * kThreads * 4;      // scale-pair ring
@@ -214,7 +220,7 @@ struct Ring {
 template <int FMT, int B, int DEPTH>
 __device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __half *xs, const int *sexp,
                          unsigned char *ring_base, int y_dtype) {
-    using R_ = Ring<B, DEPTH>;
+    using R_ = Ring<FMT, B, DEPTH>;
     constexpr int T = R_::T;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = p.K, N = p.N, XS = xs_halves(K);
@@ -396,11 +402,11 @@ struct SmemLayout {
     unsigned char *ring;
 };
 
-template <int B, int DEPTH>
+template <int FMT, int B, int DEPTH>
 __device__ __forceinline__ SmemLayout carve(unsigned char *smem, int maxK) {
     SmemLayout L;
     L.ring = smem;  // 16-byte aligned slots first
-    L.xs = reinterpret_cast<__half *>(smem + Ring<B, DEPTH>::kBytes);
+    L.xs = reinterpret_cast<__half *>(smem + Ring<FMT, B, DEPTH>::kBytes);
     L.sred = reinterpret_cast<float *>(L.xs + (size_t)B * xs_halves(maxK));
     L.sexp = reinterpret_cast<int *>(L.sred + kWarps);
     return L;
@@ -409,9 +415,9 @@ __device__ __forceinline__ SmemLayout carve(unsigned char *smem, int maxK) {
 template <int FMT, int B, int DEPTH>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvProblem p, int x_dtype, int y_dtype) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const SmemLayout L = carve<B, DEPTH>(smem, p.K);
+    const SmemLayout L = carve<FMT, B, DEPTH>(smem, p.K);
     stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp);
-    constexpr int T = Tile<B>::R;
+    constexpr int T = Tile<FMT, B>::R;
     const long long nrg = (p.N + T - 1) / T;
     const int lo = (int)(nrg * blockIdx.x / gridDim.x), hi = (int)(nrg * (blockIdx.x + 1) / gridDim.x);
     cta_rows<FMT, B, DEPTH>(p, lo, hi, L.xs, L.sexp, L.ring, y_dtype);
@@ -426,7 +432,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_prob
                                                                      int maxK, int x_dtype, int y_dtype) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int s_prob;
-    const SmemLayout L = carve<B, DEPTH>(smem, maxK);
+    const SmemLayout L = carve<FMT, B, DEPTH>(smem, maxK);
     int rg = cta_first[blockIdx.x];
     const int rg_end = cta_first[blockIdx.x + 1];
     int pi = 0;
@@ -454,9 +460,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_prob
     }
 }
 
-template <int B, int DEPTH>
+template <int FMT, int B, int DEPTH>
 static size_t gemv_smem_bytes(int K) {
-    return (size_t)Ring<B, DEPTH>::kBytes + (size_t)B * xs_halves(K) * 2 + kWarps * 4 + 8 * 4;
+    return (size_t)Ring<FMT, B, DEPTH>::kBytes + (size_t)B * xs_halves(K) * 2 + kWarps * 4 + 8 * 4;
 }
 
 }  // namespace jq
@@ -485,11 +491,11 @@ static const size_t kMaxSmem = 227 * 1024;
 
 template <int FMT, int B, int DEPTH>
 static int launch_gemv_d(const GemvProblem &p, int x_dtype, int y_dtype, cudaStream_t st) {
-    const size_t smem = gemv_smem_bytes<B, DEPTH>(p.K);
+    const size_t smem = gemv_smem_bytes<FMT, B, DEPTH>(p.K);
     if (smem > kMaxSmem) return JQ_ERR_UNSUPPORTED;
     auto kern = gemv_kernel<FMT, B, DEPTH>;
     JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const int row_groups = (p.N + Tile<B>::R - 1) / Tile<B>::R;
+    const int row_groups = (p.N + Tile<FMT, B>::R - 1) / Tile<FMT, B>::R;
     int grid = jq_sm_count();  // one persistent CTA per SM
     const int need = (row_groups + kWarps - 1) / kWarps;
     if (grid > need) grid = need;
@@ -500,18 +506,19 @@ static int launch_gemv_d(const GemvProblem &p, int x_dtype, int y_dtype, cudaStr
 // deepest prefetch ring that fits beside the staged activation
 template <int FMT, int B>
 static int launch_gemv(const GemvProblem &p, int x_dtype, int y_dtype, cudaStream_t st) {
-    if (gemv_smem_bytes<B, 4>(p.K) <= kMaxSmem) return launch_gemv_d<FMT, B, 4>(p, x_dtype, y_dtype, st);
+    if (gemv_smem_bytes<FMT, B, 4>(p.K) <= kMaxSmem) return launch_gemv_d<FMT, B, 4>(p, x_dtype, y_dtype, st);
     return launch_gemv_d<FMT, B, 2>(p, x_dtype, y_dtype, st);
 }
 
-template <int B>
-static bool gemv_fits(int K) { return gemv_smem_bytes<B, 2>(K) <= kMaxSmem; }
+template <int FMT, int B>
+static bool gemv_fits(int K) { return gemv_smem_bytes<FMT, B, 2>(K) <= kMaxSmem; }
 
+template <int FMT>
 static bool gemv_fits_b(int B, int K) {
     switch (B) {
-        case 1: return gemv_fits<1>(K); case 2: return gemv_fits<2>(K); case 3: return gemv_fits<3>(K);
-        case 4: return gemv_fits<4>(K); case 5: return gemv_fits<5>(K); case 6: return gemv_fits<6>(K);
-        case 7: return gemv_fits<7>(K); case 8: return gemv_fits<8>(K); default: return false;
+        case 1: return gemv_fits<FMT, 1>(K); case 2: return gemv_fits<FMT, 2>(K); case 3: return gemv_fits<FMT, 3>(K);
+        case 4: return gemv_fits<FMT, 4>(K); case 5: return gemv_fits<FMT, 5>(K); case 6: return gemv_fits<FMT, 6>(K);
+        case 7: return gemv_fits<FMT, 7>(K); case 8: return gemv_fits<FMT, 8>(K); default: return false;
     }
 }
 
@@ -524,8 +531,8 @@ template <int FMT>
 static int dispatch_gemv(const GemvProblem &p, int B, int x_dtype, int y_dtype, cudaStream_t st) {
     if (B > 8) return JQ_ERR_UNSUPPORTED;
     int bc = B;
-    while (bc > 1 && !gemv_fits_b(bc, p.K)) --bc;
-    if (!gemv_fits_b(bc, p.K)) return JQ_ERR_UNSUPPORTED;
+    while (bc > 1 && !gemv_fits_b<FMT>(bc, p.K)) --bc;
+    if (!gemv_fits_b<FMT>(bc, p.K)) return JQ_ERR_UNSUPPORTED;
     const size_t xe = x_dtype == JQ_F32 ? 4 : 2, ye = y_dtype == JQ_F32 ? 4 : 2;
     for (int b0 = 0; b0 < B; b0 += bc) {
         GemvProblem q = p;
@@ -589,22 +596,24 @@ extern "C" size_t jq_grouped_plan_bytes(int n) {
     return ((size_t)kPlanHeader + (size_t)(n + 1) + (size_t)jq_sm_count() + 1) * sizeof(int);
 }
 
-template <int B>
-static int plan_rows() { return Tile<B>::R; }
-
-static int tile_rows(int B) {
+template <int FMT>
+static int tile_rows_f(int B) {
     switch (B) {
-        case 1: return plan_rows<1>(); case 2: return plan_rows<2>(); case 3: return plan_rows<3>();
-        case 4: return plan_rows<4>(); case 5: return plan_rows<5>(); case 6: return plan_rows<6>();
-        case 7: return plan_rows<7>(); case 8: return plan_rows<8>(); default: return 0;
+        case 1: return Tile<FMT, 1>::R; case 2: return Tile<FMT, 2>::R; case 3: return Tile<FMT, 3>::R;
+        case 4: return Tile<FMT, 4>::R; case 5: return Tile<FMT, 5>::R; case 6: return Tile<FMT, 6>::R;
+        case 7: return Tile<FMT, 7>::R; case 8: return Tile<FMT, 8>::R; default: return 0;
     }
+}
+
+static int tile_rows(int fmt, int B) {
+    return fmt == JQ_FMT_GF4 ? tile_rows_f<JQ_FMT_GF4>(B) : tile_rows_f<JQ_FMT_E2M1>(B);
 }
 
 extern "C" int jq_grouped_plan(int fmt, const jq_problem *ph, int n, int B, void *plan_host, size_t plan_bytes) {
     if (!ph || !plan_host) return JQ_ERR_NULL_PTR;
     if (n <= 0) return JQ_ERR_BAD_SHAPE;
     if (fmt != JQ_FMT_E2M1 && fmt != JQ_FMT_GF4) return JQ_ERR_UNSUPPORTED;
-    const int R = tile_rows(B);
+    const int R = tile_rows(fmt, B);
     if (!R) return JQ_ERR_UNSUPPORTED;
     if (plan_bytes < jq_grouped_plan_bytes(n)) return JQ_ERR_WORKSPACE;
     const int grid = jq_sm_count();  // one persistent CTA per SM
@@ -658,7 +667,7 @@ template <int FMT, int B, int DEPTH>
 static int launch_grouped_d(const jq_problem *pd, const int *plan_host, const int *plan_dev, int x_dtype, int y_dtype,
                             cudaStream_t st) {
     const int n = plan_host[1], grid = plan_host[2], maxK = plan_host[3];
-    const size_t smem = gemv_smem_bytes<B, DEPTH>(maxK);
+    const size_t smem = gemv_smem_bytes<FMT, B, DEPTH>(maxK);
     if (smem > kMaxSmem) return JQ_ERR_UNSUPPORTED;
     auto kern = gemv_grouped_kernel<FMT, B, DEPTH>;
     JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -669,7 +678,7 @@ static int launch_grouped_d(const jq_problem *pd, const int *plan_host, const in
 template <int FMT, int B>
 static int launch_grouped(const jq_problem *pd, const int *plan_host, const int *plan_dev, int x_dtype, int y_dtype,
                           cudaStream_t st) {
-    if (gemv_smem_bytes<B, 4>(plan_host[3]) <= kMaxSmem)
+    if (gemv_smem_bytes<FMT, B, 4>(plan_host[3]) <= kMaxSmem)
         return launch_grouped_d<FMT, B, 4>(pd, plan_host, plan_dev, x_dtype, y_dtype, st);
     return launch_grouped_d<FMT, B, 2>(pd, plan_host, plan_dev, x_dtype, y_dtype, st);
 }
