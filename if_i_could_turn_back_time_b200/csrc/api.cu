@@ -36,10 +36,3 @@ extern "C" const char *jq_strerror(int status) {
     return "unknown status";
 }
 
-extern "C" size_t jq_workspace_bytes(int op, int N, int K, int B) {
-    (void)N; (void)K; (void)B;
-    switch (op) {
-        case JQ_OP_GEMV: return 0;
-        default: return 0;
-    }
-}

@@ -20,7 +20,21 @@ struct GemvProblem {
     const float *bias;
     void *y;
     int N, K, g, had;
+    // leading dimensions, so that a K-tile of a wider matrix is itself a problem
+    int ldw;        // bytes between packed rows
+    int lds;        // scales between rows
+    int ldx;        // activations between batch rows
+    const void *x_full;  // whole activation rows (x_full[b*ldx + k], k < K_full): the normalisation sees all of K
+    int K_full;
 };
+
+__host__ __device__ inline void finish_problem(GemvProblem &p) {
+    p.ldw = jq_row_stride_codes(p.K) >> 1;
+    p.lds = p.g ? p.K / p.g : 0;
+    p.ldx = p.K;
+    p.x_full = p.x;
+    p.K_full = p.K;
+}
 
 #ifndef JQ_THREADS
 #define JQ_THREADS 512
@@ -70,7 +84,7 @@ __device__ void stage_activation(const GemvProblem &p, int x_dtype, __half *xs, 
     const int K = p.K, XS = xs_halves(K);
     for (int b = 0; b < B; ++b) {
         float m = 0.f;
-        for (int k = tid; k < K; k += kThreads) m = fmaxf(m, fabsf(load_act(p.x, (size_t)b * K + k, x_dtype)));
+        for (int k = tid; k < p.K_full; k += kThreads) m = fmaxf(m, fabsf(load_act(p.x_full, (size_t)b * p.ldx + k, x_dtype)));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         if (lane == 0) sred[warp] = m;
@@ -90,7 +104,7 @@ __device__ void stage_activation(const GemvProblem &p, int x_dtype, __half *xs, 
                 float v[4];
                 const int k0 = blk * 128 + lane * 4;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = load_act(p.x, (size_t)b * K + k0 + j, x_dtype) * down;
+                for (int j = 0; j < 4; ++j) v[j] = load_act(p.x, (size_t)b * p.ldx + k0 + j, x_dtype) * down;
                 fwht128_warp(v, lane);
                 __half2 h01 = __floats2half2_rn(v[0], v[1]), h23 = __floats2half2_rn(v[2], v[3]);
                 uint2 pk = make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
@@ -98,7 +112,7 @@ __device__ void stage_activation(const GemvProblem &p, int x_dtype, __half *xs, 
             }
         } else {
             for (int k = tid; k < K; k += kThreads)
-                xb[xs_pos(k)] = __float2half_rn(load_act(p.x, (size_t)b * K + k, x_dtype) * down);
+                xb[xs_pos(k)] = __float2half_rn(load_act(p.x, (size_t)b * p.ldx + k, x_dtype) * down);
         }
         for (int k = K + tid; k < XS; k += kThreads) xb[xs_pos(k)] = __float2half_rn(0.f);
     }
@@ -224,10 +238,10 @@ __device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __hal
     constexpr int T = R_::T;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = p.K, N = p.N, XS = xs_halves(K);
-    const int stride_b = jq_row_stride_codes(K) >> 1;
+    const int stride_b = p.ldw;
     const int nchunks = jq_row_stride_codes(K) >> 5;
     const int nit = (nchunks + 31) >> 5;
-    const int ngroups = p.g ? K / p.g : 0;
+    const int ngroups = p.lds;
     const int gq = p.g >> 5;                             // chunks per scale group
     const bool gpow2 = p.g && (gq & (gq - 1)) == 0;
     const int gshift = p.g ? (31 - __clz(gq)) : 0;
@@ -451,6 +465,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_prob
         p.codebook = reinterpret_cast<const __half *>(jp.codebook);
         p.x = jp.x; p.bias = jp.bias; p.y = jp.y;
         p.N = jp.N; p.K = jp.K; p.g = jp.g; p.had = jp.had_block;
+        finish_problem(p);
         stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp);
         const int base = rg_start[pi];
         const int lim = min(rg_end, rg_start[pi + 1]);
@@ -525,24 +540,95 @@ static bool gemv_fits_b(int B, int K) {
 template <int FMT>
 static int dispatch_gemv_one(const GemvProblem &p, int B, int x_dtype, int y_dtype, cudaStream_t st);
 
-// Batches whose staged activation does not fit in shared memory are run as
-// several launches over sub-batches.
+namespace jq {
+// y[b][n] = sum_t part[t][b][n] + bias[n], cast to the output type.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ part, int nt, int B, int N,
+                                                            const float *__restrict__ bias, void *__restrict__ y,
+                                                            int y_dtype) {
+    const long long total = (long long)B * N;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        float acc = 0.f;
+        for (int t = 0; t < nt; ++t) acc += part[(size_t)t * total + i];
+        if (bias) acc += bias[i % N];
+        store_out(y, (size_t)i, acc, y_dtype);
+    }
+}
+}  // namespace jq
+
+// K-tile (codes) used when a batch's staged activation does not fit in shared
+// memory: the largest multiple of 1024 codes that fits, 0 if even that fails.
 template <int FMT>
-static int dispatch_gemv(const GemvProblem &p, int B, int x_dtype, int y_dtype, cudaStream_t st) {
+static int splitk_tile(int B, int K, int g) {
+    int tile = 0;
+    for (int t = 1024; t < K; t += 1024) {
+        if (!gemv_fits_b<FMT>(B, t)) break;
+        if (g == 0 || t % g == 0) tile = t;
+    }
+    return tile;
+}
+
+// A batch whose staged activation does not fit in shared memory runs as
+// split-K: one launch per K-tile writes fp32 partial outputs into the caller's
+// workspace ([tiles][B][N] floats) and a small kernel sums them.  Without a
+// workspace it falls back to several launches over sub-batches (which re-reads
+// the weights once per sub-batch).
+template <int FMT>
+static int dispatch_gemv(const GemvProblem &p, int B, int x_dtype, int y_dtype, void *ws, size_t ws_bytes,
+                         cudaStream_t st) {
     if (B > 8) return JQ_ERR_UNSUPPORTED;
+    if (gemv_fits_b<FMT>(B, p.K)) return dispatch_gemv_one<FMT>(p, B, x_dtype, y_dtype, st);
+    const size_t xe = x_dtype == JQ_F32 ? 4 : 2, ye = y_dtype == JQ_F32 ? 4 : 2;
+    const int tile = splitk_tile<FMT>(B, p.K, p.g);
+    if (tile > 0 && ws) {
+        const int nt = (p.K + tile - 1) / tile;
+        const size_t need = (size_t)nt * B * p.N * sizeof(float);
+        if (ws_bytes < need) return JQ_ERR_WORKSPACE;
+        if (reinterpret_cast<uintptr_t>(ws) & 15u) return JQ_ERR_BAD_ALIGN;
+        for (int t = 0; t < nt; ++t) {
+            const int k0 = t * tile;
+            GemvProblem q = p;
+            q.K = p.K - k0 < tile ? p.K - k0 : tile;
+            q.qw = p.qw + (k0 >> 1);
+            q.scales = p.g ? p.scales + k0 / p.g : nullptr;
+            q.x = reinterpret_cast<const char *>(p.x) + (size_t)k0 * xe;
+            q.bias = nullptr;
+            q.y = reinterpret_cast<float *>(ws) + (size_t)t * B * p.N;
+            int st_ = dispatch_gemv_one<FMT>(q, B, x_dtype, JQ_F32, st);
+            if (st_) return st_;
+        }
+        const long long total = (long long)B * p.N;
+        int blocks = (int)((total + 255) / 256);
+        if (blocks > jq_sm_count() * 8) blocks = jq_sm_count() * 8;
+        splitk_reduce_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const float *>(ws), nt, B, p.N, p.bias, p.y, y_dtype);
+        return jq_launch_status();
+    }
     int bc = B;
     while (bc > 1 && !gemv_fits_b<FMT>(bc, p.K)) --bc;
     if (!gemv_fits_b<FMT>(bc, p.K)) return JQ_ERR_UNSUPPORTED;
-    const size_t xe = x_dtype == JQ_F32 ? 4 : 2, ye = y_dtype == JQ_F32 ? 4 : 2;
     for (int b0 = 0; b0 < B; b0 += bc) {
         GemvProblem q = p;
         const int nb = B - b0 < bc ? B - b0 : bc;
-        q.x = reinterpret_cast<const char *>(p.x) + (size_t)b0 * p.K * xe;
+        q.x = reinterpret_cast<const char *>(p.x) + (size_t)b0 * p.ldx * xe;
+        q.x_full = reinterpret_cast<const char *>(p.x_full) + (size_t)b0 * p.ldx * xe;
         q.y = reinterpret_cast<char *>(p.y) + (size_t)b0 * p.N * ye;
         int st_ = dispatch_gemv_one<FMT>(q, nb, x_dtype, y_dtype, st);
         if (st_) return st_;
     }
     return JQ_OK;
+}
+
+extern "C" size_t jq_workspace_bytes(int op, int N, int K, int B) {
+    if (op != JQ_OP_GEMV || N <= 0 || K <= 0 || B <= 0 || B > 8) return 0;
+    if (gemv_fits_b<JQ_FMT_E2M1>(B, K) && gemv_fits_b<JQ_FMT_GF4>(B, K)) return 0;
+    int tile = splitk_tile<JQ_FMT_E2M1>(B, K, 0);
+    const int tile2 = splitk_tile<JQ_FMT_GF4>(B, K, 0);
+    if (tile2 < tile) tile = tile2;
+    if (tile <= 0) return 0;
+    // (a group size that does not divide the tile shrinks it; such calls answer
+    // JQ_ERR_WORKSPACE and the caller may retry without a workspace)
+    const int nt = (K + tile - 1) / tile;
+    return (size_t)nt * B * N * sizeof(float);
 }
 
 template <int FMT>
@@ -563,27 +649,29 @@ static int dispatch_gemv_one(const GemvProblem &p, int B, int x_dtype, int y_dty
 extern "C" int jq_gemv_e2m1(const void *qweight, const void *scales, const void *x, const float *bias, void *y,
                             int N, int K, int B, int g, int had_block, int x_dtype, int y_dtype, void *workspace,
                             size_t workspace_bytes, jq_stream_t stream) {
-    (void)workspace; (void)workspace_bytes;
     int st = validate_problem(JQ_FMT_E2M1, qweight, scales, nullptr, x, y, N, K, g, had_block);
     if (st) return st;
     if (B < 1) return JQ_ERR_BAD_SHAPE;
     if (!dtype_ok(x_dtype) || !dtype_ok(y_dtype)) return JQ_ERR_BAD_DTYPE;
     GemvProblem p{reinterpret_cast<const uint8_t *>(qweight), reinterpret_cast<const __half *>(scales), nullptr, x,
                   bias, y, N, K, g, had_block};
-    return dispatch_gemv<JQ_FMT_E2M1>(p, B, x_dtype, y_dtype, reinterpret_cast<cudaStream_t>(stream));
+    finish_problem(p);
+    return dispatch_gemv<JQ_FMT_E2M1>(p, B, x_dtype, y_dtype, workspace, workspace_bytes,
+                                      reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int jq_gemv_gf4(const void *qweight, const void *scales, const void *codebook, const void *x,
                            const float *bias, void *y, int N, int K, int B, int g, int had_block, int x_dtype,
                            int y_dtype, void *workspace, size_t workspace_bytes, jq_stream_t stream) {
-    (void)workspace; (void)workspace_bytes;
     int st = validate_problem(JQ_FMT_GF4, qweight, scales, codebook, x, y, N, K, g, had_block);
     if (st) return st;
     if (B < 1) return JQ_ERR_BAD_SHAPE;
     if (!dtype_ok(x_dtype) || !dtype_ok(y_dtype)) return JQ_ERR_BAD_DTYPE;
     GemvProblem p{reinterpret_cast<const uint8_t *>(qweight), reinterpret_cast<const __half *>(scales),
                   reinterpret_cast<const __half *>(codebook), x, bias, y, N, K, g, had_block};
-    return dispatch_gemv<JQ_FMT_GF4>(p, B, x_dtype, y_dtype, reinterpret_cast<cudaStream_t>(stream));
+    finish_problem(p);
+    return dispatch_gemv<JQ_FMT_GF4>(p, B, x_dtype, y_dtype, workspace, workspace_bytes,
+                                     reinterpret_cast<cudaStream_t>(stream));
 }
 
 // ---- grouped launch ---------------------------------------------------------

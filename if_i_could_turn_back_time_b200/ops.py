@@ -73,12 +73,21 @@ def _linear_rows(x2, qweight, scales, codebook, bias, fmt_id, N, K, g, had, out_
         for b0 in range(0, Bt, MAX_GEMV_BATCH):
             b1 = min(Bt, b0 + MAX_GEMV_BATCH)
             xs, ys = x2[b0:b1], y[b0:b1]
-            if fmt_id == _lib.JQ_FMT_E2M1:
-                st = lib.jq_gemv_e2m1(_ptr(qweight), _ptr(scales), _ptr(xs), _ptr(bias), _ptr(ys), N, K, b1 - b0, g,
-                                      had, _DT[x2.dtype], _DT[y.dtype], None, 0, _stream())
-            else:
-                st = lib.jq_gemv_gf4(_ptr(qweight), _ptr(scales), _ptr(codebook), _ptr(xs), _ptr(bias), _ptr(ys), N,
-                                     K, b1 - b0, g, had, _DT[x2.dtype], _DT[y.dtype], None, 0, _stream())
+            # split-K scratch (fp32 partial outputs) when the staged batch would not fit in shared memory
+            wsb = lib.jq_workspace_bytes(0, N, K, b1 - b0)
+            ws = torch.empty(wsb, dtype=torch.uint8, device=x2.device) if wsb else None
+
+            def call(ws_t):
+                nb = ws_t.numel() if ws_t is not None else 0
+                if fmt_id == _lib.JQ_FMT_E2M1:
+                    return lib.jq_gemv_e2m1(_ptr(qweight), _ptr(scales), _ptr(xs), _ptr(bias), _ptr(ys), N, K,
+                                            b1 - b0, g, had, _DT[x2.dtype], _DT[y.dtype], _ptr(ws_t), nb, _stream())
+                return lib.jq_gemv_gf4(_ptr(qweight), _ptr(scales), _ptr(codebook), _ptr(xs), _ptr(bias), _ptr(ys),
+                                       N, K, b1 - b0, g, had, _DT[x2.dtype], _DT[y.dtype], _ptr(ws_t), nb, _stream())
+
+            st = call(ws)
+            if st == -6 and ws is not None:   # workspace too small for this group size: sub-batch path
+                st = call(None)
             _lib.check(st, "jq_gemv")
     return y
 
@@ -157,6 +166,8 @@ class GroupedGemv:
             arr[i].y = self.ys[i].data_ptr()
             arr[i].N, arr[i].K, arr[i].g, arr[i].had_block = w.N, w.K, w.spec.group_size, w.spec.had_block
         self._problems_host = arr
+        self._per_problem = False
+        self.launches_per_run = 1
         with torch.cuda.device(self.device):
             nbytes = lib.jq_grouped_plan_bytes(n)
             self._plan_host = np.zeros((nbytes + 3) // 4, dtype=np.int32)
@@ -168,7 +179,15 @@ class GroupedGemv:
 
     def run(self) -> None:
         lib = _lib.load()
-        with torch.cuda.device(self.device):
-            st = lib.jq_gemv_grouped(_ptr(self._problems_dev), self._plan_host.ctypes.data, _ptr(self._plan_dev),
-                                     _DT[self.x_dtype], _DT[self.x_dtype], _stream())
-        _lib.check(st, "jq_gemv_grouped")
+        if not self._per_problem:
+            with torch.cuda.device(self.device):
+                st = lib.jq_gemv_grouped(_ptr(self._problems_dev), self._plan_host.ctypes.data, _ptr(self._plan_dev),
+                                         _DT[self.x_dtype], _DT[self.x_dtype], _stream())
+            if st != -5:
+                _lib.check(st, "jq_gemv_grouped")
+                return
+            # batch x K too large for one staged activation per CTA: one (split-K) launch per matrix instead
+            self._per_problem = True
+        for w, x, y, b in zip(self.weights, self.xs, self.ys, self.biases):
+            y.copy_(linear(x, w, b))
+        self.launches_per_run = None

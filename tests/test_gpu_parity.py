@@ -198,6 +198,26 @@ def test_leading_dims_and_large_batch_split():
     assert formats.rel_err(y.reshape(21, 96).cpu().numpy(), y1.cpu().numpy()) < 1e-6
 
 
+def test_split_k_large_batch_times_k():
+    """B x K too large to stage in shared memory: runs as split-K through a
+    caller workspace of fp32 partials; must agree with the oracle and with the
+    workspace-free sub-batch path."""
+    from if_i_could_turn_back_time_b200 import _lib
+    lib = _lib.load()
+    N, K, B = 96, 28672, 8
+    assert lib.jq_workspace_bytes(0, N, K, B) > 0 and lib.jq_workspace_bytes(0, N, 4096, 1) == 0
+    for fmt, g in (("e2m1", 32), ("gf4", 128)):
+        pw = jq.pack_weight(_weights(N, K, 5), jq.QuantSpec(fmt, g, 128))
+        gen = torch.Generator("cpu").manual_seed(3)
+        x = torch.randn(B, K, generator=gen).bfloat16()
+        bias = torch.randn(N, generator=gen)
+        _check_gemv(pw, x, bias)
+        pwd, xd, bd = pw.to(DEV), x.to(DEV), bias.to(DEV)
+        y_ws = ops.linear(xd, pwd, bd, out_dtype=torch.float32)
+        y_sub = torch.cat([ops.linear(xd[i:i + 2], pwd, bd, out_dtype=torch.float32) for i in range(0, B, 2)])
+        assert formats.rel_err(y_ws.cpu().numpy(), y_sub.cpu().numpy()) < 2e-6
+
+
 # ---------------------------------------------------------------- grouped ----
 @pytest.mark.parametrize("fmt,g,had,B", [("gf4", 128, 128, 1), ("e2m1", 32, 0, 2), ("gf4", 128, 128, 4)])
 def test_grouped_launch_equals_single_launches(fmt, g, had, B):
