@@ -30,6 +30,7 @@ extern "C" const char *jq_strerror(int status) {
         case JQ_ERR_WORKSPACE: return "workspace too small";
         case JQ_ERR_TIMEOUT: return "device-side wait gave up";
         case JQ_ERR_NOMEM: return "host allocation failed";
+        case JQ_ERR_SCRATCH_LIMIT: return "problem needs more than the library's built-in scratch array (JQ_NOALLOC_SCRATCH_BYTES)";
         default: break;
     }
     if (status <= JQ_ERR_CUDA_BASE) return cudaGetErrorString((cudaError_t)(JQ_ERR_CUDA_BASE - status));

@@ -798,3 +798,64 @@ extern "C" int jq_gemv_grouped(const jq_problem *problems_dev, const void *plan_
     if (fmt == JQ_FMT_E2M1) return dispatch_grouped<JQ_FMT_E2M1>(B, problems_dev, ph, pdv, x_dtype, y_dtype, st);
     return dispatch_grouped<JQ_FMT_GF4>(B, problems_dev, ph, pdv, x_dtype, y_dtype, st);
 }
+
+// ---- allocation-free entry point ---------------------------------------------
+// Split-K partial outputs for callers that can neither allocate device memory
+// nor lend a workspace (allocator hooks, fixed-footprint real-time loops): the
+// scratch is this file-scope device array.  In host code the symbol is only a
+// stand-in for the device object, so its device address is fetched once per
+// device with cudaGetSymbolAddress and that pointer is what the kernels get.
+static __device__ __align__(256) unsigned char jq_noalloc_scratch[JQ_NOALLOC_SCRATCH_BYTES];
+
+#include <mutex>
+static int noalloc_scratch_address(void **out) {
+    static void *addr[64];
+    static bool known[64];
+    static std::mutex mu;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return JQ_ERR_CUDA_BASE - (int)e;
+    if (dev < 0 || dev >= 64) return JQ_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!known[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, jq_noalloc_scratch);  // the current device's copy of the array
+        if (e != cudaSuccess) return JQ_ERR_CUDA_BASE - (int)e;
+        if (!p) return JQ_ERR_NULL_PTR;
+        addr[dev] = p;
+        known[dev] = true;
+    }
+    *out = addr[dev];
+    return JQ_OK;
+}
+
+template <int FMT>
+static int gemv_noalloc(const GemvProblem &p, int B, int x_dtype, int y_dtype, cudaStream_t st) {
+    if (B > 8) return JQ_ERR_UNSUPPORTED;
+    if (gemv_fits_b<FMT>(B, p.K)) return dispatch_gemv<FMT>(p, B, x_dtype, y_dtype, nullptr, 0, st);  // no scratch needed
+    const int tile = splitk_tile<FMT>(B, p.K, p.g);
+    if (tile <= 0) return JQ_ERR_UNSUPPORTED;
+    const size_t nt = (size_t)((p.K + tile - 1) / tile);
+    if (nt * (size_t)B * (size_t)p.N * sizeof(float) > (size_t)JQ_NOALLOC_SCRATCH_BYTES) return JQ_ERR_SCRATCH_LIMIT;
+    void *scratch = nullptr;
+    int s = noalloc_scratch_address(&scratch);
+    if (s) return s;
+    return dispatch_gemv<FMT>(p, B, x_dtype, y_dtype, scratch, JQ_NOALLOC_SCRATCH_BYTES, st);
+}
+
+extern "C" int jq_gemv_noalloc(int fmt, const void *qweight, const void *scales, const void *codebook, const void *x,
+                               const float *bias, void *y, int N, int K, int B, int g, int had_block, int x_dtype,
+                               int y_dtype, jq_stream_t stream) {
+    if (fmt != JQ_FMT_E2M1 && fmt != JQ_FMT_GF4) return JQ_ERR_UNSUPPORTED;
+    int st = validate_problem(fmt, qweight, scales, fmt == JQ_FMT_GF4 ? codebook : nullptr, x, y, N, K, g, had_block);
+    if (st) return st;
+    if (B < 1) return JQ_ERR_BAD_SHAPE;
+    if (!dtype_ok(x_dtype) || !dtype_ok(y_dtype)) return JQ_ERR_BAD_DTYPE;
+    GemvProblem p{reinterpret_cast<const uint8_t *>(qweight), reinterpret_cast<const __half *>(scales),
+                  fmt == JQ_FMT_GF4 ? reinterpret_cast<const __half *>(codebook) : nullptr, x, bias, y, N, K, g,
+                  had_block};
+    finish_problem(p);
+    cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+    return fmt == JQ_FMT_GF4 ? gemv_noalloc<JQ_FMT_GF4>(p, B, x_dtype, y_dtype, cs)
+                             : gemv_noalloc<JQ_FMT_E2M1>(p, B, x_dtype, y_dtype, cs);
+}

@@ -52,6 +52,7 @@ extern "C" {
 #define JQ_ERR_WORKSPACE (-6)
 #define JQ_ERR_TIMEOUT (-7)
 #define JQ_ERR_NOMEM (-8)
+#define JQ_ERR_SCRATCH_LIMIT (-9)
 #define JQ_ERR_CUDA_BASE (-1000) /* JQ_ERR_CUDA_BASE - cudaError_t */
 
 /* element types of activations / outputs */
@@ -110,6 +111,35 @@ int jq_gemv_gf4(const void *qweight, const void *scales_or_null, const void *cod
                 const void *x, const float *bias_or_null, void *y, int N, int K, int B,
                 int g, int had_block, int x_dtype, int y_dtype, void *workspace,
                 size_t workspace_bytes, jq_stream_t stream);
+
+/* The same operator for callers that must not allocate device memory and
+ * have no buffer of their own to lend as a workspace: code running inside a
+ * memory-pool callback or an allocator hook, a real-time loop whose memory was
+ * fixed at start-up, a host that only hands this library the tensors of the
+ * layer.  Such a caller cannot call cudaMalloc (it may deadlock on the
+ * allocator it is being called from, or break a latency or footprint
+ * guarantee) and cannot size a torch workspace either.  When the batch needs
+ * the split-K path (B x K too large to stage in shared memory), this entry
+ * keeps the fp32 partial outputs in a fixed array compiled into the library
+ * (JQ_NOALLOC_SCRATCH_BYTES, 8 MiB per GPU, held from library load to
+ * process exit) instead of a caller workspace.  fmt is JQ_FMT_E2M1 or
+ * JQ_FMT_GF4 (codebook NULL for E2M1); the other arguments are those of
+ * jq_gemv_*.  It has no counterpart in the reference.
+ *   - Limit: tiles * B * N * 4 bytes must fit the array, otherwise
+ *     JQ_ERR_SCRATCH_LIMIT is returned and nothing is launched.
+ *   - The first call on each device looks up the array's device address
+ *     (a driver query, not an allocation); make that first call outside any
+ *     stream capture.
+ *   - All calls on a device share the one array.  Every word a call reads
+ *     from it was written earlier in the same call, so nothing has to be
+ *     cleared between calls; but two calls whose kernels may overlap on the
+ *     GPU (different streams, no ordering) race on it.  Serialise them.
+ *   - No cudaMalloc, cudaFree or allocating library routine is called. */
+#define JQ_NOALLOC_SCRATCH_BYTES (8u << 20)
+int jq_gemv_noalloc(int fmt, const void *qweight, const void *scales_or_null,
+                    const void *codebook_or_null, const void *x, const float *bias_or_null,
+                    void *y, int N, int K, int B, int g, int had_block, int x_dtype,
+                    int y_dtype, jq_stream_t stream);
 
 /* One entry of a grouped launch: an independent GEMV problem. */
 typedef struct jq_problem {
