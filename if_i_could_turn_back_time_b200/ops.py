@@ -18,6 +18,9 @@ from .spec import QuantSpec
 
 _DT = {torch.float32: _lib.JQ_F32, torch.float16: _lib.JQ_F16, torch.bfloat16: _lib.JQ_BF16}
 MAX_GEMV_BATCH = 8
+MAX_TC_BATCH = 64
+TC_MIN_BATCH = 9          # from here on E2M1 g32 goes to the tensor-core kernel
+_last_tc_workspace = None  # kept for status inspection (ops.tc_status())
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -65,10 +68,39 @@ def fwht_block(x: torch.Tensor, block: int = 128) -> torch.Tensor:
 _OUT = {-1: None, _lib.JQ_F32: torch.float32, _lib.JQ_F16: torch.float16, _lib.JQ_BF16: torch.bfloat16}
 
 
+def tc_eligible(fmt_id: int, K: int, g: int, batch: int) -> bool:
+    return fmt_id == _lib.JQ_FMT_E2M1 and g == 32 and K % 256 == 0 and batch >= TC_MIN_BATCH
+
+
+def tc_status() -> int:
+    """Status word of the most recent tensor-core call (synchronises)."""
+    if _last_tc_workspace is None:
+        return 0
+    return _lib.load().jq_tc_status(_ptr(_last_tc_workspace), _stream())
+
+
+def _linear_rows_tc(x2, qweight, scales, bias, N, K, had, y):
+    global _last_tc_workspace
+    lib = _lib.load()
+    Bt = x2.shape[0]
+    with torch.cuda.device(x2.device):
+        for b0 in range(0, Bt, MAX_TC_BATCH):
+            b1 = min(Bt, b0 + MAX_TC_BATCH)
+            wsb = lib.jq_workspace_bytes(1, N, K, b1 - b0)
+            ws = torch.empty(wsb, dtype=torch.uint8, device=x2.device)
+            st = lib.jq_gemm_e2m1_tc(_ptr(qweight), _ptr(scales), _ptr(x2[b0:b1]), _ptr(bias), _ptr(y[b0:b1]), N, K,
+                                     b1 - b0, 32, had, _DT[x2.dtype], _DT[y.dtype], _ptr(ws), wsb, _stream())
+            _lib.check(st, "jq_gemm_e2m1_tc")
+            _last_tc_workspace = ws
+    return y
+
+
 def _linear_rows(x2, qweight, scales, codebook, bias, fmt_id, N, K, g, had, out_id=-1):
     lib = _lib.load()
     Bt = x2.shape[0]
     y = torch.empty((Bt, N), dtype=_OUT[out_id] or x2.dtype, device=x2.device)
+    if tc_eligible(fmt_id, K, g, Bt):
+        return _linear_rows_tc(x2, qweight, scales, bias, N, K, had, y)
     with torch.cuda.device(x2.device):
         for b0 in range(0, Bt, MAX_GEMV_BATCH):
             b1 = min(Bt, b0 + MAX_GEMV_BATCH)

@@ -141,6 +141,30 @@ int jq_gemv_noalloc(int fmt, const void *qweight, const void *scales_or_null,
                     void *y, int N, int K, int B, int g, int had_block, int x_dtype,
                     int y_dtype, jq_stream_t stream);
 
+/* Batched form on the tensor cores (tcgen05, kind::f8f6f4) for E2M1 weights
+ * with g = 32 and 1 <= B <= 64 (meant for B >= 9; K % 256 == 0).  Replaces
+ * the same F.linear(x, W_bar, bias) of Quantization_Experiments/layers.py:38
+ * when the reference's evaluation loop feeds whole batches
+ * (Python_Jenks_Test/Jenks_Tests/QuantNetworkTest.py:229-241, batch 128).
+ * One K = 32 MMA per scale group into its own fp32 accumulator in tensor
+ * memory; the fp16 group scale is applied by the epilogue in fp32.  The
+ * activation is represented by a sum of E4M3 terms after a power-of-two
+ * normalisation per batch row (2 terms for unrotated bf16 input = exact,
+ * otherwise 3 terms = 12 significant bits).  workspace must hold
+ * jq_workspace_bytes(JQ_OP_GEMM_TC, N, K, B) bytes (16-byte aligned); its
+ * first word receives a status (see jq_tc_status). */
+int jq_gemm_e2m1_tc(const void *qweight, const void *scales, const void *x,
+                    const float *bias_or_null, void *y, int N, int K, int B, int g,
+                    int had_block, int x_dtype, int y_dtype, void *workspace,
+                    size_t workspace_bytes, jq_stream_t stream);
+
+/* Status word the last jq_gemm_e2m1_tc on this workspace left behind: 0, or
+ * JQ_ERR_TIMEOUT if a bounded device-side wait gave up (the kernel then
+ * returned early; the device stays usable).  Synchronises the stream.  The
+ * reference's counterpart is the blocking cudaDeviceSynchronize + launch
+ * check of Python_Jenks_Test/Jenks_Tests/cuda_helpers.py:205-208. */
+int jq_tc_status(const void *workspace, jq_stream_t stream);
+
 /* One entry of a grouped launch: an independent GEMV problem. */
 typedef struct jq_problem {
     const void *qweight;

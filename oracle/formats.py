@@ -205,6 +205,33 @@ def activation_fp16_model(x: np.ndarray, had: bool) -> np.ndarray:
     return out
 
 
+def activation_e4m3_model(x: np.ndarray, had: bool, terms: int) -> np.ndarray:
+    """The values the tensor-core kernel multiplies the weights by: per batch
+    row, u = rotate(x * 2^-e) with e = exponent field of max|x| - 127 - 7
+    (- 3 with rotation), so that |u| < 256; then t1 = e4m3(u), t2 = e4m3(u -
+    t1), [t3 = e4m3(u - t1 - t2)], all round-to-nearest-even; the model value
+    is (t1 + t2 + t3) * 2^e."""
+    import torch
+    x = np.asarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    for b in range(x.shape[0]):
+        amax = np.float32(np.max(np.abs(x[b]))) if x.shape[1] else np.float32(0)
+        bits = int(amax.view(np.uint32))
+        field = (bits >> 23) & 0xFF
+        e = 0 if (field == 0xFF or (bits & 0x7FFFFFFF) == 0) else int(min(100, max(-100, field - 127 - (3 if had else 7))))
+        v = x[b:b + 1] * np.ldexp(np.float32(1.0), -e).astype(np.float32)
+        if had:
+            v = fwht_block(v, 128)
+        r = torch.from_numpy(v[0].copy())
+        tot = torch.zeros_like(r)
+        for _ in range(terms):
+            q = r.to(torch.float8_e4m3fn).to(torch.float32)
+            tot = tot + q
+            r = r - q
+        out[b] = tot.numpy() * np.ldexp(np.float32(1.0), e).astype(np.float32)
+    return out
+
+
 def rel_err(y: np.ndarray, y_ref: np.ndarray) -> float:
     """max|y - y_ref| / max|y_ref| over the whole output."""
     y = np.asarray(y, dtype=np.float64)

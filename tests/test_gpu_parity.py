@@ -218,6 +218,53 @@ def test_split_k_large_batch_times_k():
         assert formats.rel_err(y_ws.cpu().numpy(), y_sub.cpu().numpy()) < 2e-6
 
 
+# ------------------------------------------------------- tensor-core path ----
+def _check_tc(pw, x_cpu, bias_cpu=None):
+    pwd = pw.to(DEV)
+    w_hat = _oracle_dequant(pw)
+    x32 = x_cpu.float().numpy()
+    b32 = None if bias_cpu is None else bias_cpu.numpy()
+    had = bool(pw.spec.had_block)
+    assert ops.tc_eligible(pw.spec.fmt_id, pw.K, pw.spec.group_size, x_cpu.shape[0])
+    y = ops.linear(x_cpu.to(DEV), pwd, None if bias_cpu is None else bias_cpu.to(DEV), out_dtype=torch.float32)
+    assert ops.tc_status() == 0, "a device-side wait timed out"
+    y = y.cpu().numpy()
+    ref = formats.linear_ref(x32, w_hat, b32, had_block=pw.spec.had_block)
+    err = formats.rel_err(y, ref)
+    assert err <= TOL, f"rel err {err:.3e} vs fp32 oracle"
+    terms = 2 if (not had and x_cpu.dtype == torch.bfloat16) else 3
+    ref_m = formats.linear_ref(formats.activation_e4m3_model(x32, had, terms), w_hat, b32)
+    err_m = formats.rel_err(y, ref_m)
+    assert err_m <= 1e-5, f"rel err {err_m:.3e} vs E4M3-term activation model"
+    return err
+
+
+@pytest.mark.parametrize("B", [9, 16, 17, 32, 33, 64])
+def test_tensor_core_path_batches(B):
+    pw = jq.pack_weight(_weights(300, 1024, 21), jq.QuantSpec("e2m1", 32, 0))
+    gen = torch.Generator("cpu").manual_seed(B)
+    _check_tc(pw, torch.randn(B, 1024, generator=gen).bfloat16(), torch.randn(300, generator=gen))
+
+
+@pytest.mark.parametrize("N,K,had,dtype", [(128, 256, 0, torch.bfloat16), (1, 512, 128, torch.bfloat16),
+                                            (257, 4096, 0, torch.float32), (4096, 4096, 0, torch.bfloat16),
+                                            (1024, 8192, 128, torch.float16)])
+def test_tensor_core_path_shapes(N, K, had, dtype):
+    pw = jq.pack_weight(_weights(N, K, N + K), jq.QuantSpec("e2m1", 32, had))
+    gen = torch.Generator("cpu").manual_seed(N)
+    _check_tc(pw, torch.randn(16, K, generator=gen).to(dtype))
+    _check_tc(pw, (torch.randn(40, K, generator=gen) * 1e-4).to(dtype))
+
+
+def test_tensor_core_path_large_batch_is_split_and_matches_gemv():
+    pw = jq.pack_weight(_weights(512, 1024, 3), jq.QuantSpec("e2m1", 32, 0)).to(DEV)
+    x = torch.randn(130, 1024, generator=torch.Generator("cpu").manual_seed(2)).bfloat16().to(DEV)
+    y_tc = ops.linear(x, pw, out_dtype=torch.float32)
+    assert ops.tc_status() == 0
+    y_cc = torch.cat([ops.linear(x[i:i + 8], pw, out_dtype=torch.float32) for i in range(0, 130, 8)])
+    assert formats.rel_err(y_tc.cpu().numpy(), y_cc.cpu().numpy()) <= 1e-5  # both exact up to fp32 summation
+
+
 # ---------------------------------------------------------------- grouped ----
 @pytest.mark.parametrize("fmt,g,had,B", [("gf4", 128, 128, 1), ("e2m1", 32, 0, 2), ("gf4", 128, 128, 4)])
 def test_grouped_launch_equals_single_launches(fmt, g, had, B):
