@@ -23,27 +23,36 @@
 
 namespace jqtc {
 
-constexpr int kThreads = 256;
+#ifndef JQ_TC_X
+#define JQ_TC_X 0   // timing experiments only: 1 = no MMAs, 2 = no weight copies, 4 = no epilogue reads
+#endif
+constexpr int kThreads = 384;   // 4 service warps + 8 epilogue warps
 constexpr int kTileM = 128;
 constexpr int kHeaderBytes = 512;      // workspace: int status, int exponent[64]
 constexpr uint32_t kSpinLimit = 1u << 22;
 
-template <int BN>
+template <int BN, int TERMS>
 struct Cfg {
-    static constexpr int G = (256 / BN) < 8 ? (256 / BN) : 8;  // 32-code groups per stage (and per accumulator buffer)
+    static constexpr int G = (256 / BN) < 8 ? (256 / BN) : 8;  // 32-code groups per stage = accumulators per buffer
     static constexpr int SK = G * 32;                          // codes of K per stage
-    static constexpr int A_BYTES = 2 * G * kTileM * 16;        // padded FP4: 16 codes per 16-byte chunk
-    static constexpr int ACC_COLS = G * BN;                    // fp32 accumulator columns per buffer
-    static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
+    // padded FP4: 16 codes per 16-byte chunk; one chunk column = 128 rows x 16 B, plus 16 B so that the 16
+    // lanes that copy one row's 16 chunks do not all hit the same shared-memory bank
+    static constexpr int A_CHUNK = kTileM * 16 + 16;
+    static constexpr int A_BYTES = 2 * G * A_CHUNK;
+    static constexpr int B_BYTES = TERMS * G * 2 * BN * 16;    // [term][group][chunk][column][16 B]
+    static constexpr int ACC_COLS = G * BN;                    // fp32 accumulator columns per buffer (<= 256)
+    static constexpr int TMEM_COLS = 512;
 };
 
+constexpr int kScaleBytes = kTileM * 16;  // per stage: 16 bytes (up to 8 fp16 group scales) per weight row
+
 template <int BN, int TERMS>
-__host__ __device__ constexpr int b_bytes() { return TERMS * Cfg<BN>::G * 2 * BN * 16; }
+__host__ __device__ constexpr int stage_bytes() { return Cfg<BN, TERMS>::A_BYTES + Cfg<BN, TERMS>::B_BYTES + kScaleBytes; }
 
 template <int BN, int TERMS>
 __host__ __device__ constexpr int stages() {
     // as many stages as fit in ~200 KB, at most 6
-    return (200 * 1024) / (Cfg<BN>::A_BYTES + b_bytes<BN, TERMS>()) > 6 ? 6 : (200 * 1024) / (Cfg<BN>::A_BYTES + b_bytes<BN, TERMS>());
+    return (200 * 1024) / stage_bytes<BN, TERMS>() > 6 ? 6 : (200 * 1024) / stage_bytes<BN, TERMS>();
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -65,7 +74,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try(bar, parity)) return true;
         if (*err) return false;
-        if (i > 32) __nanosleep(128);
+        if (i > 8192) __nanosleep(64);  // back off only when the wait is clearly long: a sleeping waiter wakes late
     }
     *err = JQ_ERR_TIMEOUT;
     return false;
@@ -110,19 +119,34 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// tcgen05.ld of N consecutive fp32 columns of this thread's lane; the data is valid after tmem_wait()
 template <int N>
-__device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&v)[N]);
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[N]);
 template <>
-__device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
+__device__ __forceinline__ void tmem_ld<8>(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+template <>
+__device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+template <>
+__device__ __forceinline__ void tmem_ld<32>(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---- activation preparation -----------------------------------------------------
 // x[B,K] -> (rotate) -> u = x * 2^-e with max|u| < 256 -> t1 = e4m3(u),
@@ -147,7 +171,7 @@ __device__ __forceinline__ float e4m3_round(float v, uint8_t &byte) {
 template <int BN, int TERMS>
 __global__ void __launch_bounds__(256) tc_prepare_kernel(const void *__restrict__ x, int B, int K, int had, int x_dtype,
                                                           unsigned char *__restrict__ ws) {
-    constexpr int G = Cfg<BN>::G, SK = Cfg<BN>::SK;
+    constexpr int G = Cfg<BN, TERMS>::G, SK = Cfg<BN, TERMS>::SK;
     __shared__ float sred[8];
     __shared__ int sexp;
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -208,13 +232,15 @@ struct TcArgs {
     void *y;
     unsigned char *ws;
     int N, K, B, y_dtype;
+    int kparts;     // K is cut into this many equal parts, one work item per (row tile, part)
+    float *parts;   // [kparts][B][N] fp32 partial outputs when kparts > 1
 };
 
 template <int BN, int TERMS>
 __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, TERMS>;
     constexpr int G = C::G, SK = C::SK, S = stages<BN, TERMS>();
-    constexpr int A_BYTES = C::A_BYTES, B_BYTES = b_bytes<BN, TERMS>();
+    constexpr int A_BYTES = C::A_BYTES, B_BYTES = C::B_BYTES, STAGE = stage_bytes<BN, TERMS>();
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t bars[2 * 6 + 4];
     __shared__ uint32_t s_tmem;
@@ -229,17 +255,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
     if (tid == 0) {
         s_err = 0;
         for (int s = 0; s < S; ++s) {
-            mbar_init(full0 + 8 * s, 64);   // 32 lanes of each producer warp, arriving through cp.async completion
-            mbar_init(empty0 + 8 * s, 1);   // one tcgen05.commit
+            mbar_init(full0 + 8 * s, 96);   // 32 lanes of each of the 3 producer warps, arriving through cp.async completion
+            mbar_init(empty0 + 8 * s, 9);   // one tcgen05.commit + the 8 epilogue warps (they read the scale tile)
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(tfull0 + 8 * i, 1);   // one tcgen05.commit
-            mbar_init(tempty0 + 8 * i, 4);  // one arrival per epilogue warp
+            mbar_init(tempty0 + 8 * i, 8);  // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // the upper 8 bytes of every FP4 chunk are padding that no copy writes: keep them defined
-    for (uint32_t i = tid; i < (uint32_t)(S * (A_BYTES + B_BYTES)) / 16; i += kThreads)
+    for (uint32_t i = tid; i < (uint32_t)(S * STAGE) / 16; i += kThreads)
         asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(smem_base + i * 16), "r"(0u) : "memory");
     if (warp == 3) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(C::TMEM_COLS) : "memory");
@@ -251,63 +277,78 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
     const uint32_t tmem = s_tmem;
 
     const int ntiles = (a.N + kTileM - 1) / kTileM;
-    const int nst = a.K / SK;           // stages per row tile
-    const int ldw = a.K >> 1;           // bytes per packed row (K % 32 == 0 here)
+    const int nst = (a.K / SK) / a.kparts;   // stages per work item
+    const int nitems = ntiles * a.kparts;    // item = tile * kparts + part
+    const int ldw = a.K >> 1;                // bytes per packed row (K % 32 == 0 here)
     const int ngroups = a.K >> 5;
     const unsigned char *xq = a.ws + kHeaderBytes;
 
-    if (warp == 0) {
-        // ---- weight producer: lane = row inside a 32-row block
+    if (warp < 2) {
+        // ---- weight producers: two warps, 64 rows each.  16 lanes copy the 16 chunks (8 B) of one row's
+        //      stage slice, so global reads coalesce; two rows per instruction.
         uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < ntiles && !*err; tile += gridDim.x) {
+        const int c = lane & 15, rsub = lane >> 4;
+        for (int item = blockIdx.x; item < nitems && !*err; item += gridDim.x) {
+            const int tile = item / a.kparts, part = item % a.kparts;
             for (int st = 0; st < nst; ++st, ++it) {
                 const int s = it % S;
                 if (!mbar_wait(empty0 + 8 * s, ((it / S) & 1) ^ 1, err)) break;
-                const uint32_t dstA = smem_base + s * (A_BYTES + B_BYTES);
-#pragma unroll
-                for (int rb = 0; rb < 4; ++rb) {
-                    const int r = rb * 32 + lane;
-                    const int row = min(tile * kTileM + r, a.N - 1);
-                    const uint8_t *src = a.qw + (size_t)row * ldw + (size_t)st * (SK / 2);
-#pragma unroll
-                    for (int c = 0; c < 2 * G; ++c) cp_async8(dstA + c * (kTileM * 16) + r * 16, src + c * 8);
+                const uint32_t dstA = smem_base + s * STAGE + c * C::A_CHUNK;
+                const size_t koff = (size_t)(part * nst + st) * (SK / 2) + c * 8;
+                if (c < 2 * G && !(JQ_TC_X & 2)) {
+#pragma unroll 8
+                    for (int rr = 0; rr < 32; ++rr) {
+                        const int r = warp * 64 + rr * 2 + rsub;
+                        const int row = min(tile * kTileM + r, a.N - 1);
+                        cp_async8(dstA + r * 16, a.qw + (size_t)row * ldw + koff);
+                    }
                 }
                 cp_async_arrive(full0 + 8 * s);
             }
         }
-    } else if (warp == 1) {
-        // ---- activation producer: the stage's tile is one contiguous block of the prepared buffer
+    } else if (warp == 2) {
+        // ---- activation + scale producer: the stage's activation tile is one contiguous block of the prepared buffer
         uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < ntiles && !*err; tile += gridDim.x) {
+        for (int item = blockIdx.x; item < nitems && !*err; item += gridDim.x) {
+            const int tile = item / a.kparts, part = item % a.kparts;
             for (int st = 0; st < nst; ++st, ++it) {
                 const int s = it % S;
                 if (!mbar_wait(empty0 + 8 * s, ((it / S) & 1) ^ 1, err)) break;
-                const uint32_t dstB = smem_base + s * (A_BYTES + B_BYTES) + A_BYTES;
-                const unsigned char *src = xq + (size_t)st * B_BYTES;
+                const uint32_t dstB = smem_base + s * STAGE + A_BYTES;
+                const unsigned char *src = xq + (size_t)(part * nst + st) * B_BYTES;
                 for (int i = lane; i < B_BYTES / 16; i += 32) cp_async16(dstB + i * 16, src + (size_t)i * 16);
+                // the tile's group scales: G fp16 per row, to 16 bytes per row
+#pragma unroll
+                for (int rr = 0; rr < 4; ++rr) {
+                    const int r = rr * 32 + lane;
+                    const int row = min(tile * kTileM + r, a.N - 1);
+                    const __half *sp = a.scales + (size_t)row * ngroups + (size_t)(part * nst + st) * G;
+                    if (G == 8) cp_async16(dstB + B_BYTES + r * 16, sp);
+                    else cp_async8(dstB + B_BYTES + r * 16, sp);
+                }
                 cp_async_arrive(full0 + 8 * s);
             }
         }
-    } else if (warp == 2) {
-        // ---- MMA issuer (one thread)
+    } else if (warp == 3) {
+        // ---- MMA issuer (one thread): per 32-code group, TERMS MMAs (K = 32 each) into the group's accumulator
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc(kTileM, BN);
             uint32_t it = 0;
-            for (int tile = blockIdx.x; tile < ntiles && !*err; tile += gridDim.x) {
+            for (int item = blockIdx.x; item < nitems && !*err; item += gridDim.x) {
                 for (int st = 0; st < nst; ++st, ++it) {
                     const int s = it % S, ab = it & 1;
                     if (!mbar_wait(tempty0 + 8 * ab, ((it >> 1) & 1) ^ 1, err)) break;  // accumulator buffer drained
                     if (!mbar_wait(full0 + 8 * s, (it / S) & 1, err)) break;            // tiles landed
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     tc_fence_after();
-                    const uint32_t sa = smem_base + s * (A_BYTES + B_BYTES), sb = sa + A_BYTES;
+                    const uint32_t sa = smem_base + s * STAGE, sb = sa + A_BYTES;
 #pragma unroll
                     for (int g = 0; g < G; ++g) {
-                        const uint64_t ad = smem_desc(sa + g * (2 * kTileM * 16), kTileM * 16, 128);
+                        const uint64_t ad = smem_desc(sa + g * (2 * C::A_CHUNK), C::A_CHUNK, 128);
 #pragma unroll
                         for (int t = 0; t < TERMS; ++t) {
                             const uint64_t bd = smem_desc(sb + (t * G + g) * (2 * BN * 16), BN * 16, 128);
-                            mma_f8f6f4(tmem + ab * C::ACC_COLS + g * BN, ad, bd, idesc, t > 0 ? 1u : 0u);
+                            if (!(JQ_TC_X & 1)) mma_f8f6f4(tmem + ab * 256 + g * BN, ad, bd, idesc, t > 0 ? 1u : 0u);
                         }
                     }
                     mma_commit(empty0 + 8 * s);    // smem stage reusable once these MMAs have read it
@@ -315,40 +356,49 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
                 }
             }
         }
-    } else if (warp >= 4) {
-        // ---- epilogue: thread = one accumulator lane = one weight row of the tile
+    } else {
+        // ---- epilogue, 8 warps: thread = one accumulator lane (weight row) x one half of the batch columns.
+        //      The read of group g+1 from tensor memory is in flight while group g is scaled and added.
         const int q = warp & 3;                // tensor-memory lane quarter this warp may touch
+        const int h = (warp - 4) >> 2;         // which half of the columns
+        constexpr int CH = BN / 2;
         const int r = q * 32 + lane;
         const int *hdr = reinterpret_cast<const int *>(a.ws);
         uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < ntiles && !*err; tile += gridDim.x) {
+        for (int item = blockIdx.x; item < nitems && !*err; item += gridDim.x) {
+            const int tile = item / a.kparts, part = item % a.kparts;
             const int row = tile * kTileM + r;
-            const int rowc = min(row, a.N - 1);
-            float acc[BN];
+            float acc[CH];
 #pragma unroll
-            for (int b = 0; b < BN; ++b) acc[b] = 0.f;
+            for (int b = 0; b < CH; ++b) acc[b] = 0.f;
             bool ok = true;
             for (int st = 0; st < nst; ++st, ++it) {
-                const int ab = it & 1;
-                // this row's G scales of the stage (contiguous fp16)
-                float sc[G];
-                {
-                    const __half *sp = a.scales + (size_t)rowc * ngroups + (size_t)st * G;
-#pragma unroll
-                    for (int g = 0; g < G; ++g) sc[g] = __half2float(sp[g]);
-                }
+                const int s = it % S, ab = it & 1;
                 ok = __all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * ab, (it >> 1) & 1, err));  // warp-uniform outcome
                 if (!ok) break;
                 tc_fence_after();
+                const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + ab * 256 + h * CH;
+                uint32_t d[2][CH];
+                tmem_ld<CH>(tbase, d[0]);
+                float sc[G];  // this row's G scales of the stage, staged in shared memory by the producer
+                {
+                    const uint32_t sp = smem_base + s * STAGE + A_BYTES + B_BYTES + r * 16;
+                    uint32_t w[4];
+                    if (G == 8) asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(sp));
+                    else asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(sp));
 #pragma unroll
-                for (int g = 0; g < G; ++g) {
+                    for (int g = 0; g < G; ++g)
+                        sc[g] = __half2float(__ushort_as_half((uint16_t)((g & 1) ? (w[g >> 1] >> 16) : (w[g >> 1] & 0xffffu))));
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + 8 * s);  // scale tile consumed
+                tmem_wait();
 #pragma unroll
-                    for (int c0 = 0; c0 < BN; c0 += 16) {
-                        float d[16];
-                        tmem_ld<16>(tmem + ((uint32_t)(q * 32) << 16) + ab * C::ACC_COLS + g * BN + c0, d);
+                for (int g = 0; g < ((JQ_TC_X & 4) ? 1 : G); ++g) {
+                    if (g + 1 < G) tmem_ld<CH>(tbase + (g + 1) * BN, d[(g + 1) & 1]);
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(d[i], sc[g], acc[c0 + i]);
-                    }
+                    for (int i = 0; i < CH; ++i) acc[i] = fmaf(__uint_as_float(d[g & 1][i]), sc[g], acc[i]);
+                    if (g + 1 < G) tmem_wait();
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -356,12 +406,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
             }
             if (!ok) break;
             if (row < a.N) {
-                const float bias = a.bias ? a.bias[row] : 0.f;
+                const float bias = (a.bias && a.kparts == 1) ? a.bias[row] : 0.f;
 #pragma unroll
-                for (int b = 0; b < BN; ++b) {
+                for (int i = 0; i < CH; ++i) {
+                    const int b = h * CH + i;
                     if (b < a.B) {
                         const float up = __uint_as_float((uint32_t)(127 + hdr[1 + b]) << 23);
-                        jq::store_out(a.y, (size_t)b * a.N + row, fmaf(acc[b], up, bias), a.y_dtype);
+                        const float v = fmaf(acc[i], up, bias);
+                        if (a.kparts == 1) jq::store_out(a.y, (size_t)b * a.N + row, v, a.y_dtype);
+                        else a.parts[((size_t)part * a.B + b) * a.N + row] = v;
                     }
                 }
             }
@@ -379,25 +432,50 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
     }
 }
 
-template <int BN, int TERMS>
-static size_t tc_ws_bytes(int K) { return (size_t)kHeaderBytes + (size_t)TERMS * K * BN; }
+// y[b][n] = sum_p parts[p][b][n] + bias[n]
+__global__ void __launch_bounds__(256) tc_reduce_kernel(const float *__restrict__ parts, int np, int B, int N,
+                                                        const float *__restrict__ bias, void *__restrict__ y, int y_dtype) {
+    const long long total = (long long)B * N;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        float acc = 0.f;
+        for (int p = 0; p < np; ++p) acc += parts[(size_t)p * total + i];
+        if (bias) acc += bias[i % N];
+        jq::store_out(y, (size_t)i, acc, y_dtype);
+    }
+}
+
+constexpr int kMaxKParts = 8;
 
 template <int BN, int TERMS>
-static int launch_tc(const TcArgs &a, const void *x, int had, int x_dtype, cudaStream_t st) {
-    using C = Cfg<BN>;
+static int launch_tc(TcArgs a, const void *x, int had, int x_dtype, cudaStream_t st) {
+    using C = Cfg<BN, TERMS>;
     if (a.K % C::SK) return JQ_ERR_UNSUPPORTED;
+    // enough work items for every SM: cut K while the stage count divides evenly
+    {
+        const int ntiles_ = (a.N + kTileM - 1) / kTileM, nst_all = a.K / C::SK, sms = jq_sm_count();
+        int kp = 1;
+        while (kp < kMaxKParts && ntiles_ * kp < sms && nst_all % (kp * 2) == 0 && nst_all / (kp * 2) >= 4) kp *= 2;
+        a.kparts = kp;
+        a.parts = reinterpret_cast<float *>(a.ws + kHeaderBytes + ((size_t)3 * a.K * BN + 255) / 256 * 256);
+    }
     constexpr int S = stages<BN, TERMS>();
     static_assert(S >= 2 && S <= 6, "stage count");
-    const size_t smem = (size_t)S * (C::A_BYTES + b_bytes<BN, TERMS>()) + 128;
+    const size_t smem = (size_t)S * stage_bytes<BN, TERMS>() + 128;
     tc_prepare_kernel<BN, TERMS><<<BN, 256, 0, st>>>(x, a.B, a.K, had, x_dtype, a.ws);
     int s = jq_launch_status();
     if (s) return s;
     auto kern = gemm_e2m1_tc_kernel<BN, TERMS>;
     JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const int ntiles = (a.N + kTileM - 1) / kTileM;
+    const int nitems = ((a.N + kTileM - 1) / kTileM) * a.kparts;
     int grid = jq_sm_count();
-    if (grid > ntiles) grid = ntiles;
+    if (grid > nitems) grid = nitems;
     kern<<<grid, kThreads, smem, st>>>(a);
+    s = jq_launch_status();
+    if (s || a.kparts == 1) return s;
+    const long long total = (long long)a.B * a.N;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > jq_sm_count() * 8) blocks = jq_sm_count() * 8;
+    tc_reduce_kernel<<<blocks, 256, 0, st>>>(a.parts, a.kparts, a.B, a.N, a.bias, a.y, a.y_dtype);
     return jq_launch_status();
 }
 
@@ -409,9 +487,11 @@ static int tc_bn(int B) { return B <= 16 ? 16 : (B <= 32 ? 32 : 64); }
 // bf16 has 8 significant bits = two E4M3 terms exactly; anything else gets three
 static int tc_terms(int had, int x_dtype) { return (!had && x_dtype == JQ_BF16) ? 2 : 3; }
 
-size_t jq_tc_workspace_bytes(int K, int B) {
-    if (B < 1 || B > 64 || K <= 0) return 0;
-    return (size_t)kHeaderBytes + (size_t)3 * K * tc_bn(B);
+// header | prepared activation (3 terms x K x columns) | split-K partials
+size_t jq_tc_workspace_bytes(int N, int K, int B) {
+    if (B < 1 || B > 64 || K <= 0 || N <= 0) return 0;
+    const size_t xq = ((size_t)3 * K * tc_bn(B) + 255) / 256 * 256;
+    return (size_t)kHeaderBytes + xq + (size_t)kMaxKParts * B * N * sizeof(float);
 }
 
 extern "C" int jq_gemm_e2m1_tc(const void *qweight, const void *scales, const void *x, const float *bias, void *y,
@@ -424,9 +504,9 @@ extern "C" int jq_gemm_e2m1_tc(const void *qweight, const void *scales, const vo
     if (K % 256 || (had_block && K % 128)) return JQ_ERR_UNSUPPORTED;
     if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return JQ_ERR_BAD_DTYPE;
     if (!jq_aligned16(qweight) || !jq_aligned16(scales) || !jq_aligned16(workspace)) return JQ_ERR_BAD_ALIGN;
-    if (workspace_bytes < jq_tc_workspace_bytes(K, B)) return JQ_ERR_WORKSPACE;
+    if (workspace_bytes < jq_tc_workspace_bytes(N, K, B)) return JQ_ERR_WORKSPACE;
     TcArgs a{reinterpret_cast<const uint8_t *>(qweight), reinterpret_cast<const __half *>(scales), bias, y,
-             reinterpret_cast<unsigned char *>(workspace), N, K, B, y_dtype};
+             reinterpret_cast<unsigned char *>(workspace), N, K, B, y_dtype, 1, nullptr};
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int bn = tc_bn(B), terms = tc_terms(had_block, x_dtype);
     if (bn == 16) return terms == 2 ? launch_tc<16, 2>(a, x, had_block, x_dtype, st) : launch_tc<16, 3>(a, x, had_block, x_dtype, st);

@@ -79,6 +79,20 @@ def tc_status() -> int:
     return _lib.load().jq_tc_status(_ptr(_last_tc_workspace), _stream())
 
 
+_ws_cache = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """Grow-only scratch per (device, stream): calls on one stream are ordered,
+    so consecutive calls may share it; another stream gets its own."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    t = _ws_cache.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _ws_cache[key] = t
+    return t
+
+
 def _linear_rows_tc(x2, qweight, scales, bias, N, K, had, y):
     global _last_tc_workspace
     lib = _lib.load()
@@ -87,7 +101,7 @@ def _linear_rows_tc(x2, qweight, scales, bias, N, K, had, y):
         for b0 in range(0, Bt, MAX_TC_BATCH):
             b1 = min(Bt, b0 + MAX_TC_BATCH)
             wsb = lib.jq_workspace_bytes(1, N, K, b1 - b0)
-            ws = torch.empty(wsb, dtype=torch.uint8, device=x2.device)
+            ws = _workspace(x2.device, wsb)
             st = lib.jq_gemm_e2m1_tc(_ptr(qweight), _ptr(scales), _ptr(x2[b0:b1]), _ptr(bias), _ptr(y[b0:b1]), N, K,
                                      b1 - b0, 32, had, _DT[x2.dtype], _DT[y.dtype], _ptr(ws), wsb, _stream())
             _lib.check(st, "jq_gemm_e2m1_tc")
@@ -107,7 +121,7 @@ def _linear_rows(x2, qweight, scales, codebook, bias, fmt_id, N, K, g, had, out_
             xs, ys = x2[b0:b1], y[b0:b1]
             # split-K scratch (fp32 partial outputs) when the staged batch would not fit in shared memory
             wsb = lib.jq_workspace_bytes(0, N, K, b1 - b0)
-            ws = torch.empty(wsb, dtype=torch.uint8, device=x2.device) if wsb else None
+            ws = _workspace(x2.device, wsb)[:wsb] if wsb else None
 
             def call(ws_t):
                 nb = ws_t.numel() if ws_t is not None else 0
@@ -149,8 +163,17 @@ def linear(x: torch.Tensor, pw: PackedWeight, bias: Optional[torch.Tensor] = Non
     _need_cuda(x, pw.qweight, pw.scales, pw.codebook, bias)
     if bias is not None and bias.dtype != torch.float32:
         bias = bias.float()
-    return torch.ops.jq.linear(x, pw.qweight, pw.scales, pw.codebook, bias, pw.spec.fmt_id, pw.N, pw.K,
-                               pw.spec.group_size, pw.spec.had_block, -1 if out_dtype is None else _DT[out_dtype])
+    out_id = -1 if out_dtype is None else _DT[out_dtype]
+    if torch.compiler.is_compiling():
+        # through the dispatcher so that tracing sees one opaque op with a fake implementation
+        return torch.ops.jq.linear(x, pw.qweight, pw.scales, pw.codebook, bias, pw.spec.fmt_id, pw.N, pw.K,
+                                   pw.spec.group_size, pw.spec.had_block, out_id)
+    x2 = x.reshape(-1, pw.K)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = _linear_rows(x2, pw.qweight, pw.scales, pw.codebook, bias, pw.spec.fmt_id, pw.N, pw.K, pw.spec.group_size,
+                     pw.spec.had_block, out_id)
+    return y.reshape(*x.shape[:-1], pw.N)
 
 
 class GroupedGemv:
@@ -200,6 +223,11 @@ class GroupedGemv:
         self._problems_host = arr
         self._per_problem = False
         self.launches_per_run = 1
+        if batch > MAX_GEMV_BATCH:
+            # beyond the CUDA-core kernel's batch: one call per matrix (tensor-core path where eligible)
+            self._per_problem = True
+            self.launches_per_run = None
+            return
         with torch.cuda.device(self.device):
             nbytes = lib.jq_grouped_plan_bytes(n)
             self._plan_host = np.zeros((nbytes + 3) // 4, dtype=np.int32)

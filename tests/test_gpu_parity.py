@@ -195,7 +195,9 @@ def test_leading_dims_and_large_batch_split():
     y = ops.linear(x, pw)
     assert y.shape == (3, 7, 96)
     y1 = torch.cat([ops.linear(x.reshape(21, 256)[i:i + 1], pw) for i in range(21)])
-    assert formats.rel_err(y.reshape(21, 96).cpu().numpy(), y1.cpu().numpy()) < 1e-6
+    # 21 rows go through the tensor-core kernel (E4M3-term activation), single rows through the GEMV
+    # (fp16 activation): both are within the gate of the oracle, hence within 2x of each other
+    assert formats.rel_err(y.reshape(21, 96).cpu().numpy(), y1.cpu().numpy()) < 2 * TOL
 
 
 def test_split_k_large_batch_times_k():
