@@ -38,6 +38,11 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 
 HBM_NOMINAL_GBS = 8000.0
+# DRAM bytes (read + write) per algorithmic byte of the grouped GEMV kernel, from one ncu capture each on a
+# smaller case of the same kernel (profiles/gemv_grouped_gf4_11008x4096.md: 381.93 MB for 378.10 MB;
+# profiles/gemv_grouped_e2m1_8192x8192.md: 608.58 MB for 604.50 MB); traffic grows in proportion to the
+# rows processed, so a full launch's traffic is this ratio times its algorithmic bytes.
+DRAM_TRAFFIC_RATIO = {"gf4": 381.930496 / 378.101760, "e2m1": 608.581888 / 604.504064}
 
 WORKLOADS = {
     # name: (fmt, group, had_block, layers, [(label, N, K, count-per-layer)], init std)
@@ -296,10 +301,12 @@ def main():
                 "clocks": clocks,
                 "e2e": {"value": args.batch / (ms_e2e * 1e-3), "unit": "tok/s",
                         "h2d_bytes_per_step": int(x_host.numel()), "d2h_bytes_per_step": int(y_host.numel())},
-                "gpu_launches": args.steps,
+                "gpu_launches": args.steps * (grp.launches_per_run or len(weights)),
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                             "frac": achieved / peak, "frac_of_8TBs": achieved / HBM_NOMINAL_GBS, "traffic": None,
-                             "peak_source": f"{how} copy bandwidth", "kernel": "gemv_grouped_kernel",
+                             "frac": achieved / peak, "frac_of_8TBs": achieved / HBM_NOMINAL_GBS,
+                             "traffic": int(alg * DRAM_TRAFFIC_RATIO[fmt]) if args.batch <= 8 else None,
+                             "peak_source": f"{how} copy bandwidth",
+                             "kernel": "gemv_grouped_kernel" if args.batch <= 8 else "gemm_e2m1_tc_kernel (one call per matrix)",
                              "kernel_ms": k_ms, "algorithmic_bytes_per_launch": alg},
                 "pack_seconds": meta["pack_seconds"]}
         if world == 1 and not args.no_cpu_baseline:
