@@ -194,6 +194,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: all-gather fused into the GEMV epilogue (peer stores) or one NCCL all-gather per step")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
@@ -230,13 +232,28 @@ def main():
     from if_i_could_turn_back_time_b200 import ops
     threads = max(1, len(os.sched_getaffinity(0)) // max(1, world))
     weights, meta = build_stack(args.workload, rank, world, args.batch, device, threads)
-    grp = ops.GroupedGemv(weights, args.batch, torch.bfloat16)
+    exchange = "none"
+    grp = None
+    if world > 1 and args.exchange == "fused" and args.batch <= 8:
+        try:
+            grp = ops.GroupedGemv(weights, args.batch, torch.bfloat16, full_rows=[w.N * world for w in weights],
+                                  row_offsets=[w.N * rank for w in weights], group=dist.group.WORLD)
+            exchange = "fused peer stores + barrier"
+        except Exception as e:  # symmetric memory unavailable: fall back to the NCCL exchange
+            if rank == 0:
+                print(f"fused exchange unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+            grp = None
+    if grp is None:
+        grp = ops.GroupedGemv(weights, args.batch, torch.bfloat16)
+        if world > 1:
+            exchange = "nccl all_gather_into_tensor"
+    fused = grp.fused_exchange
     gen = torch.Generator("cpu").manual_seed(100)
     x_host = torch.empty(grp.x_arena.numel(), dtype=torch.uint8).pin_memory()
     x_host.view(torch.bfloat16).copy_(torch.randn(grp.x_arena.numel() // 2, generator=gen).bfloat16())
-    y_host = torch.empty(grp.y_arena.numel() * world, dtype=torch.uint8).pin_memory()
+    y_host = torch.empty(grp.y_arena.numel() * (1 if fused else world), dtype=torch.uint8).pin_memory()
     grp.x_arena.copy_(x_host)
-    y_all = torch.empty(grp.y_arena.numel() * world, dtype=torch.uint8, device=device) if world > 1 else None
+    y_all = torch.empty(grp.y_arena.numel() * world, dtype=torch.uint8, device=device) if (world > 1 and not fused) else None
 
     def barrier():
         if world > 1:
@@ -255,10 +272,12 @@ def main():
         if record:
             b.record()
             kernel_events.append((a, b))
-        if world > 1:
+        if fused:
+            grp.barrier()
+        elif world > 1:
             dist.all_gather_into_tensor(y_all, grp.y_arena)
         if e2e:
-            src = y_all if world > 1 else grp.y_arena
+            src = y_all if y_all is not None else grp.y_arena
             y_host.copy_(src, non_blocking=True)
             torch.cuda.current_stream().synchronize()   # the caller needs the result before the next token
 
@@ -308,7 +327,7 @@ def main():
                              "peak_source": f"{how} copy bandwidth",
                              "kernel": "gemv_grouped_kernel" if args.batch <= 8 else "gemm_e2m1_tc_kernel (one call per matrix)",
                              "kernel_ms": k_ms, "algorithmic_bytes_per_launch": alg},
-                "pack_seconds": meta["pack_seconds"]}
+                "pack_seconds": meta["pack_seconds"], "exchange": exchange}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_reference_leg(args.workload, args.batch, args.cpu_budget)
         print(json.dumps(line))

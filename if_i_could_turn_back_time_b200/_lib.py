@@ -26,6 +26,7 @@ class jq_problem(ctypes.Structure):
         ("qweight", c_void_p), ("scales", c_void_p), ("codebook", c_void_p),
         ("x", c_void_p), ("bias", c_void_p), ("y", c_void_p),
         ("N", c_int32), ("K", c_int32), ("g", c_int32), ("had_block", c_int32),
+        ("ldy", c_int32), ("reserved", c_int32 * 3),
     ]
 
 
@@ -47,6 +48,7 @@ _SIGNATURES = {
     "jq_grouped_plan_bytes": (c_size_t, [c_int]),
     "jq_grouped_plan": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_size_t]),
     "jq_gemv_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "jq_gemv_grouped_peers": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "jq_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "jq_pack_e2m1_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
     "jq_pack_gf4_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int]),

@@ -26,6 +26,9 @@ struct GemvProblem {
     int ldx;        // activations between batch rows
     const void *x_full;  // whole activation rows (x_full[b*ldx + k], k < K_full): the normalisation sees all of K
     int K_full;
+    int ldy;        // outputs between batch rows (N, or the unsharded N when this is a row shard)
+    int npeer;      // copies of every output element to write (1 = only the local buffer)
+    long long peer_delta[8];  // byte offsets from this rank's output buffer to each copy's buffer (peer GPUs)
 };
 
 __host__ __device__ inline void finish_problem(GemvProblem &p) {
@@ -34,6 +37,9 @@ __host__ __device__ inline void finish_problem(GemvProblem &p) {
     p.ldx = p.K;
     p.x_full = p.x;
     p.K_full = p.K;
+    p.ldy = p.N;
+    p.npeer = 1;
+    p.peer_delta[0] = 0;
 }
 
 #ifndef JQ_THREADS
@@ -383,17 +389,21 @@ __device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __hal
             for (int r = 0; r < T; ++r)
 #pragma unroll
                 for (int b = 0; b < B; ++b) acc[r][b] = warp_sum(acc[r][b]);
-            if (lane == 0) {
+            // every lane holds every sum: lane (copy c, row r) = c * T + r writes row r into copy c of the
+            // output (copy 0 is the local buffer; further copies are peer GPUs' buffers, written over NVLink)
+            {
+                const int r_l = lane % T, c_l = lane / T;
+                const int row = crg * T + r_l;
+                if (c_l < p.npeer && row < N) {
+                    const float bias = p.bias ? p.bias[row] : 0.f;
+                    void *yc = reinterpret_cast<char *>(p.y) + p.peer_delta[c_l];
 #pragma unroll
-                for (int r = 0; r < T; ++r) {
-                    const int row = crg * T + r;
-                    if (row < N) {
-                        const float bias = p.bias ? p.bias[row] : 0.f;
+                    for (int b = 0; b < B; ++b) {
+                        float v = 0.f;
 #pragma unroll
-                        for (int b = 0; b < B; ++b) {
-                            const float up = __uint_as_float((uint32_t)(127 + sexp[b]) << 23);  // 2^e
-                            store_out(p.y, (size_t)b * N + row, fmaf(acc[r][b], up, bias), y_dtype);
-                        }
+                        for (int r = 0; r < T; ++r) v = (r == r_l) ? acc[r][b] : v;
+                        const float up = __uint_as_float((uint32_t)(127 + sexp[b]) << 23);  // 2^e
+                        store_out(yc, (size_t)b * p.ldy + row, fmaf(v, up, bias), y_dtype);
                     }
                 }
             }
@@ -437,13 +447,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvProblem p, int x_
     cta_rows<FMT, B, DEPTH>(p, lo, hi, L.xs, L.sexp, L.ring, y_dtype);
 }
 
+struct PeerInfo {
+    int n;
+    long long delta[8];
+};
+
 // Grouped launch: the concatenated row-group space of all problems is split
 // into contiguous, byte-balanced CTA ranges on the host (cta_first[]); a CTA
-// re-stages the activation whenever it crosses into the next problem.
+// re-stages the activation whenever it crosses into the next problem.  With
+// peers.n > 1 every output element is also stored into the same offset of the
+// peers' output buffers (the all-gather of a row-sharded layer, fused into the
+// epilogue as plain stores over NVLink).
 template <int FMT, int B, int DEPTH>
 __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_problem *probs, int nprob,
                                                                      const int *rg_start, const int *cta_first,
-                                                                     int maxK, int x_dtype, int y_dtype) {
+                                                                     int maxK, int x_dtype, int y_dtype, PeerInfo peers) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int s_prob;
     const SmemLayout L = carve<FMT, B, DEPTH>(smem, maxK);
@@ -466,6 +484,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_prob
         p.x = jp.x; p.bias = jp.bias; p.y = jp.y;
         p.N = jp.N; p.K = jp.K; p.g = jp.g; p.had = jp.had_block;
         finish_problem(p);
+        if (jp.ldy > 0) p.ldy = jp.ldy;
+        p.npeer = peers.n;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) p.peer_delta[i] = peers.delta[i];
         stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp);
         const int base = rg_start[pi];
         const int lim = min(rg_end, rg_start[pi + 1]);
@@ -756,50 +778,66 @@ extern "C" int jq_grouped_plan(int fmt, const jq_problem *ph, int n, int B, void
 
 template <int FMT, int B, int DEPTH>
 static int launch_grouped_d(const jq_problem *pd, const int *plan_host, const int *plan_dev, int x_dtype, int y_dtype,
-                            cudaStream_t st) {
+                            const PeerInfo &peers, cudaStream_t st) {
     const int n = plan_host[1], grid = plan_host[2], maxK = plan_host[3];
     const size_t smem = gemv_smem_bytes<FMT, B, DEPTH>(maxK);
     if (smem > kMaxSmem) return JQ_ERR_UNSUPPORTED;
     auto kern = gemv_grouped_kernel<FMT, B, DEPTH>;
     JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kThreads, smem, st>>>(pd, n, plan_dev + kPlanHeader, plan_dev + kPlanHeader + n + 1, maxK, x_dtype, y_dtype);
+    kern<<<grid, kThreads, smem, st>>>(pd, n, plan_dev + kPlanHeader, plan_dev + kPlanHeader + n + 1, maxK, x_dtype, y_dtype, peers);
     return jq_launch_status();
 }
 
 template <int FMT, int B>
 static int launch_grouped(const jq_problem *pd, const int *plan_host, const int *plan_dev, int x_dtype, int y_dtype,
-                          cudaStream_t st) {
+                          const PeerInfo &peers, cudaStream_t st) {
     if (gemv_smem_bytes<FMT, B, 4>(plan_host[3]) <= kMaxSmem)
-        return launch_grouped_d<FMT, B, 4>(pd, plan_host, plan_dev, x_dtype, y_dtype, st);
-    return launch_grouped_d<FMT, B, 2>(pd, plan_host, plan_dev, x_dtype, y_dtype, st);
+        return launch_grouped_d<FMT, B, 4>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
+    return launch_grouped_d<FMT, B, 2>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
 }
 
 template <int FMT>
-static int dispatch_grouped(int B, const jq_problem *pd, const int *ph, const int *pdv, int xd, int yd, cudaStream_t st) {
+static int dispatch_grouped(int B, const jq_problem *pd, const int *ph, const int *pdv, int xd, int yd,
+                            const PeerInfo &peers, cudaStream_t st) {
     switch (B) {
-        case 1: return launch_grouped<FMT, 1>(pd, ph, pdv, xd, yd, st);
-        case 2: return launch_grouped<FMT, 2>(pd, ph, pdv, xd, yd, st);
-        case 3: return launch_grouped<FMT, 3>(pd, ph, pdv, xd, yd, st);
-        case 4: return launch_grouped<FMT, 4>(pd, ph, pdv, xd, yd, st);
-        case 5: return launch_grouped<FMT, 5>(pd, ph, pdv, xd, yd, st);
-        case 6: return launch_grouped<FMT, 6>(pd, ph, pdv, xd, yd, st);
-        case 7: return launch_grouped<FMT, 7>(pd, ph, pdv, xd, yd, st);
-        case 8: return launch_grouped<FMT, 8>(pd, ph, pdv, xd, yd, st);
+        case 1: return launch_grouped<FMT, 1>(pd, ph, pdv, xd, yd, peers, st);
+        case 2: return launch_grouped<FMT, 2>(pd, ph, pdv, xd, yd, peers, st);
+        case 3: return launch_grouped<FMT, 3>(pd, ph, pdv, xd, yd, peers, st);
+        case 4: return launch_grouped<FMT, 4>(pd, ph, pdv, xd, yd, peers, st);
+        case 5: return launch_grouped<FMT, 5>(pd, ph, pdv, xd, yd, peers, st);
+        case 6: return launch_grouped<FMT, 6>(pd, ph, pdv, xd, yd, peers, st);
+        case 7: return launch_grouped<FMT, 7>(pd, ph, pdv, xd, yd, peers, st);
+        case 8: return launch_grouped<FMT, 8>(pd, ph, pdv, xd, yd, peers, st);
         default: return JQ_ERR_UNSUPPORTED;
     }
 }
 
+extern "C" int jq_gemv_grouped_peers(const jq_problem *problems_dev, const void *plan_host, const void *plan_dev,
+                                     int x_dtype, int y_dtype, int npeer, const int64_t *peer_delta,
+                                     jq_stream_t stream);
+
 extern "C" int jq_gemv_grouped(const jq_problem *problems_dev, const void *plan_host, const void *plan_dev,
                                int x_dtype, int y_dtype, jq_stream_t stream) {
-    if (!problems_dev || !plan_host || !plan_dev) return JQ_ERR_NULL_PTR;
+    const int64_t zero = 0;
+    return jq_gemv_grouped_peers(problems_dev, plan_host, plan_dev, x_dtype, y_dtype, 1, &zero, stream);
+}
+
+extern "C" int jq_gemv_grouped_peers(const jq_problem *problems_dev, const void *plan_host, const void *plan_dev,
+                                     int x_dtype, int y_dtype, int npeer, const int64_t *peer_delta,
+                                     jq_stream_t stream) {
+    if (!problems_dev || !plan_host || !plan_dev || !peer_delta) return JQ_ERR_NULL_PTR;
+    if (npeer < 1 || npeer > 8) return JQ_ERR_BAD_SHAPE;
+    PeerInfo peers;
+    peers.n = npeer;
+    for (int i = 0; i < 8; ++i) peers.delta[i] = i < npeer ? (long long)peer_delta[i] : 0;
     const int *ph = reinterpret_cast<const int *>(plan_host);
     if (ph[0] != kPlanMagic) return JQ_ERR_BAD_SHAPE;
     if (!dtype_ok(x_dtype) || !dtype_ok(y_dtype)) return JQ_ERR_BAD_DTYPE;
     const int B = ph[5], fmt = ph[6];
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int *pdv = reinterpret_cast<const int *>(plan_dev);
-    if (fmt == JQ_FMT_E2M1) return dispatch_grouped<JQ_FMT_E2M1>(B, problems_dev, ph, pdv, x_dtype, y_dtype, st);
-    return dispatch_grouped<JQ_FMT_GF4>(B, problems_dev, ph, pdv, x_dtype, y_dtype, st);
+    if (fmt == JQ_FMT_E2M1) return dispatch_grouped<JQ_FMT_E2M1>(B, problems_dev, ph, pdv, x_dtype, y_dtype, peers, st);
+    return dispatch_grouped<JQ_FMT_GF4>(B, problems_dev, ph, pdv, x_dtype, y_dtype, peers, st);
 }
 
 // ---- allocation-free entry point ---------------------------------------------

@@ -179,10 +179,21 @@ def linear(x: torch.Tensor, pw: PackedWeight, bias: Optional[torch.Tensor] = Non
 class GroupedGemv:
     """A fixed set of independent GEMVs (one decode step's matrices) run in a
     single launch.  Inputs and outputs are preallocated; ``run()`` only
-    enqueues the kernel."""
+    enqueues the kernel.
+
+    Row-sharded use (one process per GPU): pass each matrix's local shard in
+    ``weights``, its unsharded row count in ``full_rows`` and the shard's
+    first row in ``row_offsets``; outputs are then full-width ``[batch,
+    full_rows]`` buffers of which this rank fills its columns.  With
+    ``group`` (a ``torch.distributed`` process group, world size <= 8) the
+    output arena lives in symmetric memory and the kernel's epilogue stores
+    every result into all ranks' arenas (the all-gather fused into the GEMV);
+    call ``barrier()`` after ``run()`` before reading."""
 
     def __init__(self, weights: Sequence[PackedWeight], batch: int, x_dtype=torch.bfloat16,
-                 biases: Optional[Sequence[Optional[torch.Tensor]]] = None, device=None):
+                 biases: Optional[Sequence[Optional[torch.Tensor]]] = None, device=None,
+                 full_rows: Optional[Sequence[int]] = None, row_offsets: Optional[Sequence[int]] = None,
+                 group=None):
         lib = _lib.load()
         if not weights:
             raise ValueError("no problems")
@@ -195,21 +206,36 @@ class GroupedGemv:
         self.batch = batch
         self.x_dtype = x_dtype
         self.biases = list(biases) if biases is not None else [None] * len(weights)
+        self.full_rows = list(full_rows) if full_rows is not None else [w.N for w in weights]
+        self.row_offsets = list(row_offsets) if row_offsets is not None else [0] * len(weights)
         # all inputs live in one arena and all outputs in another, so a step's
         # activations move with one copy each way; every view is 256-byte aligned
         esz = torch.empty((), dtype=x_dtype).element_size()
         rnd = lambda nbytes: (nbytes + 255) // 256 * 256
         x_off, y_off, xo, yo = [], [], 0, 0
-        for w in weights:
+        for w, nf in zip(weights, self.full_rows):
             x_off.append(xo); xo += rnd(batch * w.K * esz)
-            y_off.append(yo); yo += rnd(batch * w.N * esz)
+            y_off.append(yo); yo += rnd(batch * nf * esz)
         self.x_arena = torch.zeros(xo, dtype=torch.uint8, device=self.device)
-        self.y_arena = torch.zeros(yo, dtype=torch.uint8, device=self.device)
+        self._symm = None
+        self._peer_delta = np.zeros(1, dtype=np.int64)
+        if group is not None and torch.distributed.get_world_size(group) > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.y_arena = symm_mem.empty(yo, dtype=torch.uint8, device=self.device)
+            self.y_arena.zero_()
+            self._symm = symm_mem.rendezvous(self.y_arena, group.group_name if hasattr(group, "group_name") else group)
+            own = self.y_arena.data_ptr()
+            ptrs = [int(p) for p in self._symm.buffer_ptrs]
+            if len(ptrs) > 8:
+                raise ValueError("at most 8 peers")
+            self._peer_delta = np.array([p - own for p in ptrs], dtype=np.int64)
+        else:
+            self.y_arena = torch.zeros(yo, dtype=torch.uint8, device=self.device)
         self.x_offsets, self.y_offsets = x_off, y_off
         self.xs: List[torch.Tensor] = [
             self.x_arena[o:o + batch * w.K * esz].view(x_dtype).view(batch, w.K) for o, w in zip(x_off, weights)]
         self.ys: List[torch.Tensor] = [
-            self.y_arena[o:o + batch * w.N * esz].view(x_dtype).view(batch, w.N) for o, w in zip(y_off, weights)]
+            self.y_arena[o:o + batch * nf * esz].view(x_dtype).view(batch, nf) for o, nf in zip(y_off, self.full_rows)]
         n = len(weights)
         arr = (_lib.jq_problem * n)()
         for i, w in enumerate(weights):
@@ -218,13 +244,16 @@ class GroupedGemv:
             arr[i].codebook = w.codebook.data_ptr() if w.codebook is not None else None
             arr[i].x = self.xs[i].data_ptr()
             arr[i].bias = self.biases[i].data_ptr() if self.biases[i] is not None else None
-            arr[i].y = self.ys[i].data_ptr()
+            arr[i].y = self.ys[i].data_ptr() + self.row_offsets[i] * esz
             arr[i].N, arr[i].K, arr[i].g, arr[i].had_block = w.N, w.K, w.spec.group_size, w.spec.had_block
+            arr[i].ldy = self.full_rows[i]
         self._problems_host = arr
         self._per_problem = False
         self.launches_per_run = 1
         if batch > MAX_GEMV_BATCH:
             # beyond the CUDA-core kernel's batch: one call per matrix (tensor-core path where eligible)
+            if self._symm is not None or any(self.row_offsets):
+                raise ValueError("the fused exchange needs batch <= 8")
             self._per_problem = True
             self.launches_per_run = None
             return
@@ -237,17 +266,30 @@ class GroupedGemv:
             self._problems_dev = torch.from_numpy(raw).to(self.device)
             self._plan_dev = torch.from_numpy(self._plan_host).to(self.device)
 
+    @property
+    def fused_exchange(self) -> bool:
+        return self._symm is not None
+
+    def barrier(self) -> None:
+        """Order the ranks after run(): every rank's stores into this rank's
+        output arena are complete once this returns on the stream."""
+        if self._symm is not None:
+            self._symm.barrier()
+
     def run(self) -> None:
         lib = _lib.load()
         if not self._per_problem:
             with torch.cuda.device(self.device):
-                st = lib.jq_gemv_grouped(_ptr(self._problems_dev), self._plan_host.ctypes.data, _ptr(self._plan_dev),
-                                         _DT[self.x_dtype], _DT[self.x_dtype], _stream())
+                st = lib.jq_gemv_grouped_peers(_ptr(self._problems_dev), self._plan_host.ctypes.data,
+                                               _ptr(self._plan_dev), _DT[self.x_dtype], _DT[self.x_dtype],
+                                               len(self._peer_delta), self._peer_delta.ctypes.data, _stream())
             if st != -5:
                 _lib.check(st, "jq_gemv_grouped")
                 return
+            if self._symm is not None:
+                _lib.check(st, "jq_gemv_grouped_peers")
             # batch x K too large for one staged activation per CTA: one (split-K) launch per matrix instead
             self._per_problem = True
-        for w, x, y, b in zip(self.weights, self.xs, self.ys, self.biases):
-            y.copy_(linear(x, w, b))
+        for w, x, y, b, nf, ro in zip(self.weights, self.xs, self.ys, self.biases, self.full_rows, self.row_offsets):
+            y[:, ro:ro + w.N].copy_(linear(x, w, b))
         self.launches_per_run = None

@@ -174,6 +174,9 @@ typedef struct jq_problem {
     const float *bias;     /* NULL for none */
     void *y;
     int32_t N, K, g, had_block;
+    int32_t ldy;           /* outputs between batch rows of y; 0 means N.  A row shard of a wider layer sets
+                              this to the unsharded N and points y at its first row's column. */
+    int32_t reserved[3];   /* must be 0 */
 } jq_problem;
 
 /* Grouped launch: n independent GEMVs (same format, batch B and dtypes) in
@@ -194,6 +197,19 @@ int jq_grouped_plan(int fmt, const jq_problem *problems_host, int n, int B, void
                     size_t plan_bytes);
 int jq_gemv_grouped(const jq_problem *problems_dev, const void *plan_host, const void *plan_dev,
                     int x_dtype, int y_dtype, jq_stream_t stream);
+
+/* The grouped launch with the all-gather of a row-sharded layer fused into
+ * its epilogue: every output element is stored at the same byte offset into
+ * npeer (<= 8) output buffers, the local one (peer_delta 0) and those of the
+ * peer GPUs (peer_delta[i] = peer buffer base - local buffer base, from
+ * symmetric / peer-mapped memory), as plain stores over NVLink; no loads from
+ * peer memory, no multicast.  The caller still has to order the ranks (a
+ * barrier after the launch) before anyone reads the gathered outputs.  The
+ * reference has no multi-device path
+ * (Python_Jenks_Test/Jenks_Tests/QuantNetworkTest.py:19 picks one device). */
+int jq_gemv_grouped_peers(const jq_problem *problems_dev, const void *plan_host,
+                          const void *plan_dev, int x_dtype, int y_dtype, int npeer,
+                          const int64_t *peer_delta, jq_stream_t stream);
 
 /* Bytes of caller-provided device scratch an op needs for these sizes. */
 size_t jq_workspace_bytes(int op, int N, int K, int B);

@@ -284,6 +284,41 @@ def test_grouped_launch_equals_single_launches(fmt, g, had, B):
         assert torch.equal(y, ops.linear(x, pw))
 
 
+def test_grouped_row_shards_and_peer_copies_on_one_gpu():
+    """Two row shards of each matrix run as two grouped launches into full-width outputs; the second
+    launch also writes every result into a second buffer through the peer-copy path (here a local
+    buffer stands in for a peer GPU's).  Both must equal the unsharded result bit for bit."""
+    shapes = [(512, 1024), (96, 2048), (1000, 256)]
+    spec = jq.QuantSpec("gf4", 128, 128)
+    full = [jq.pack_weight(_weights(n, k, n + k), spec) for n, k in shapes]
+    gen = torch.Generator("cpu").manual_seed(4)
+    xs = [torch.randn(1, k, generator=gen).bfloat16() for _, k in shapes]
+    ref = [ops.linear(x.to(DEV), pw.to(DEV)) for x, pw in zip(xs, full)]
+    halves = []
+    for rank in range(2):
+        shards = [pw.rows(rank * pw.N // 2, (rank + 1) * pw.N // 2).to(DEV) for pw in full]
+        grp = ops.GroupedGemv(shards, 1, torch.bfloat16, full_rows=[pw.N for pw in full],
+                              row_offsets=[rank * pw.N // 2 for pw in full])
+        for gx, x in zip(grp.xs, xs):
+            gx.copy_(x)
+        halves.append(grp)
+    mirror = torch.zeros_like(halves[0].y_arena)
+    for rank, grp in enumerate(halves):
+        # copy 0 = this group's own arena, copy 1 = rank 0's arena (or the mirror when that is the same buffer)
+        target = mirror if rank == 0 else halves[0].y_arena
+        grp._peer_delta = np.array([0, target.data_ptr() - grp.y_arena.data_ptr()], dtype=np.int64)
+        grp.run()
+    torch.cuda.synchronize()
+    for i, r in enumerate(ref):
+        assert torch.equal(halves[0].ys[i], r)                      # own half + the half pushed by "rank 1"
+        lo = full[i].N // 2
+        assert torch.equal(halves[1].ys[i][:, lo:], r[:, lo:])
+    esz = 2
+    for i, (o, pw) in enumerate(zip(halves[0].y_offsets, full)):
+        got = mirror[o:o + pw.N * esz].view(torch.bfloat16)[: pw.N // 2]
+        assert torch.equal(got, ref[i][0, : pw.N // 2])             # rank 0's half also landed in the mirror
+
+
 # ------------------------------------------------- full-size property tests ----
 def test_full_size_4096_e2m1_and_row_permutation():
     g = torch.Generator("cpu").manual_seed(1)
