@@ -214,6 +214,17 @@ int jq_gemv_grouped_peers(const jq_problem *problems_dev, const void *plan_host,
 /* Bytes of caller-provided device scratch an op needs for these sizes. */
 size_t jq_workspace_bytes(int op, int N, int K, int B);
 
+/* Two-class Jenks natural break of an ascending-sorted fp32 array (device),
+ * O(n) with float64 prefix sums.  Replaces the O(n^2) kernel
+ * jenks_optimization_cuda of Python_Jenks_Test/Jenks_Tests/cuda_helpers.py:151-211
+ * and the host argmin / GVF of its wrapper Linear_Mask (:378-395).
+ * var_or_null (device, n doubles) receives var[i] = SSD(v[:i]) + SSD(v[i:])
+ * when given; out3 (device, 3 doubles) receives {break index (first argmin),
+ * min var, GVF = (SSD_total - min var) / (SSD_total + 1e-8)}. */
+size_t jq_jenks2_workspace_bytes(long long n);
+int jq_jenks2_break(const float *sorted, long long n, double *var_or_null, double *out3,
+                    void *workspace, size_t workspace_bytes, jq_stream_t stream);
+
 /* ---- host-side packers (CPU, multi-threaded; one-off, not the hot path) ----
  * Replace the grid/scale construction of QuantLinear.__init__
  * (Quantization_Experiments/layers.py:22-26) for the packed formats.  All

@@ -319,6 +319,40 @@ def test_grouped_row_shards_and_peer_copies_on_one_gpu():
         assert torch.equal(got, ref[i][0, : pw.N // 2])             # rank 0's half also landed in the mirror
 
 
+# ------------------------------------------------------ two-class Jenks ----
+@pytest.mark.parametrize("n", [1, 2, 7, 300, 2049, 235200])
+def test_two_class_jenks_break_matches_reference_form(n):
+    from if_i_could_turn_back_time_b200 import prune
+    from oracle import jenks as ojenks
+    g = torch.Generator("cpu").manual_seed(n)
+    v = torch.rand(n, generator=g) ** 3          # skewed scores, like |w * grad|
+    sv = v.sort().values
+    brk, vmin, gvf, var = prune.jenks2_break(sv.to(DEV), return_var=True)
+    v64 = sv.double().numpy()
+    if n <= 2049:   # the reference form is O(n^2): only small n
+        assert brk == ojenks.two_class_break_reference_form(v64)
+    # prefix-sum form in numpy float64 for every n
+    s1 = np.concatenate([[0.0], np.cumsum(v64)]); s2 = np.concatenate([[0.0], np.cumsum(v64 * v64)])
+    i = np.arange(n, dtype=np.float64)
+    lo = np.where(i > 0, s2[:-1] - s1[:-1] ** 2 / np.maximum(i, 1), 0.0)
+    hi = (s2[-1] - s2[:-1]) - (s1[-1] - s1[:-1]) ** 2 / (n - i)
+    want = lo + hi
+    got = var.cpu().numpy()
+    assert np.allclose(got, want, rtol=1e-9, atol=1e-9 * max(1.0, abs(want).max()))
+    assert abs(want[brk] - want.min()) <= 1e-9 * max(1.0, abs(want).max())
+    ssd = ((v64 - v64.mean()) ** 2).sum()
+    assert abs(gvf - (ssd - want.min()) / (ssd + 1e-8)) < 1e-9
+
+
+def test_linear_mask_like_reference():
+    from if_i_could_turn_back_time_b200 import prune
+    g = torch.Generator("cpu").manual_seed(0)
+    scores = torch.cat([torch.rand(900, generator=g) * 0.01, 1.0 + torch.rand(100, generator=g)])[torch.randperm(1000, generator=g)]
+    mask, gvf = prune.linear_mask(scores.reshape(25, 40).to(DEV))
+    assert mask.shape == (25, 40) and int(mask.sum().item()) == 100      # the upper cluster is kept
+    assert torch.equal(mask.reshape(-1).bool().cpu(), scores > 0.5) and gvf > 0.95
+
+
 # ------------------------------------------------- full-size property tests ----
 def test_full_size_4096_e2m1_and_row_permutation():
     g = torch.Generator("cpu").manual_seed(1)
