@@ -10,6 +10,7 @@ from .spec import QuantSpec, algorithmic_bytes  # noqa: F401
 from .pack import PackedWeight, pack_weight  # noqa: F401
 from . import ops  # noqa: F401
 from .linear import JenksQuantLinear, quantize_module  # noqa: F401
+from .conv import JenksQuantConv2d  # noqa: F401
 
-__all__ = ["QuantSpec", "PackedWeight", "pack_weight", "ops", "JenksQuantLinear", "quantize_module",
+__all__ = ["QuantSpec", "PackedWeight", "pack_weight", "ops", "JenksQuantLinear", "JenksQuantConv2d", "quantize_module",
            "algorithmic_bytes"]

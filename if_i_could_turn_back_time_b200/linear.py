@@ -96,6 +96,12 @@ def quantize_module(module, bitwidth: int = 4, **spec_kwargs):
     if isinstance(module, nn.Linear):
         mask = (module.weight.data != 0).float()
         return JenksQuantLinear(module, bitwidth, mask=mask, **spec_kwargs)
+    if isinstance(module, nn.Conv2d) and module.groups == 1 and not isinstance(module.padding, str):
+        from .conv import JenksQuantConv2d
+        if isinstance(module, JenksQuantConv2d):
+            return module
+        mask = (module.weight.data != 0).float()
+        return JenksQuantConv2d(module, bitwidth, mask=mask, **spec_kwargs)
     if isinstance(module, list):
         return [quantize_module(m, bitwidth, **spec_kwargs) for m in module]
     module = copy.deepcopy(module)

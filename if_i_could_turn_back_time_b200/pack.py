@@ -41,11 +41,39 @@ class PackedWeight:
         return sum(t.numel() * t.element_size() for t in (self.qweight, self.scales, self.codebook) if t is not None)
 
 
+def _gpu_packable(W: torch.Tensor, spec: QuantSpec) -> bool:
+    pg = spec.group_size // 32
+    return W.shape[1] % 32 == 0 and 1 <= pg <= 32 and pg & (pg - 1) == 0 and W.shape[1] % spec.group_size == 0
+
+
+def _pack_e2m1_cuda(W: torch.Tensor, spec: QuantSpec, rotate: bool) -> PackedWeight:
+    """E2M1 quantisation on the GPU (bit-identical to the host packer); the
+    weight-side rotation uses the same fp32 butterfly kernel as the operator."""
+    import ctypes
+    lib = _lib.load()
+    from . import ops
+    Wf = W.detach().float().contiguous()
+    N, K = Wf.shape
+    if spec.had_block and rotate:
+        if K % spec.had_block:
+            raise ValueError(f"K={K} is not a multiple of the rotation block {spec.had_block}")
+        Wf = ops.fwht_block(Wf, spec.had_block)
+    q = torch.empty((N, K // 2), dtype=torch.uint8, device=W.device)
+    s = torch.empty((N, K // spec.group_size), dtype=torch.float16, device=W.device)
+    with torch.cuda.device(W.device):
+        st = lib.jq_pack_e2m1(ctypes.c_void_p(Wf.data_ptr()), N, K, spec.group_size, ctypes.c_void_p(q.data_ptr()),
+                              ctypes.c_void_p(s.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(st, "jq_pack_e2m1")
+    return PackedWeight(spec, N, K, q, s, None)
+
+
 def pack_weight(W: torch.Tensor, spec: QuantSpec, threads: int = 0, rotate: bool = True) -> PackedWeight:
     """Quantise and pack W [N, K].  With ``spec.had_block`` the weight is first
     multiplied on the right by the block Hadamard matrix (fp32), so that
     ``W x == (W H)(H x)`` once the operator rotates x."""
     lib = _lib.load()
+    if W.is_cuda and spec.fmt == "e2m1" and _gpu_packable(W, spec):
+        return _pack_e2m1_cuda(W, spec, rotate)
     Wf = W.detach().to("cpu", torch.float32).contiguous().clone()
     N, K = Wf.shape
     g = spec.group_size

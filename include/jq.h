@@ -225,6 +225,12 @@ size_t jq_jenks2_workspace_bytes(long long n);
 int jq_jenks2_break(const float *sorted, long long n, double *var_or_null, double *out3,
                     void *workspace, size_t workspace_bytes, jq_stream_t stream);
 
+/* E2M1 packer on the device: W fp32 [N,K] (device) -> qweight, scales (device),
+ * bit-identical to jq_pack_e2m1_host.  g must be 32 * a power of two <= 1024.
+ * Same reference counterpart as the host packers below. */
+int jq_pack_e2m1(const float *W, int N, int K, int g, void *qweight, void *scales,
+                 jq_stream_t stream);
+
 /* ---- host-side packers (CPU, multi-threaded; one-off, not the hot path) ----
  * Replace the grid/scale construction of QuantLinear.__init__
  * (Quantization_Experiments/layers.py:22-26) for the packed formats.  All

@@ -319,6 +319,50 @@ def test_grouped_row_shards_and_peer_copies_on_one_gpu():
         assert torch.equal(got, ref[i][0, : pw.N // 2])             # rank 0's half also landed in the mirror
 
 
+# ----------------------------------------------------------------- conv2d ----
+@pytest.mark.parametrize("fmt,g,cin,cout,k,stride,pad", [("gf4", 0, 3, 8, 3, 1, 1), ("e2m1", 32, 32, 16, 3, 2, 1),
+                                                          ("e2m1", 32, 64, 24, 2, 1, 0), ("gf4", 128, 16, 12, 1, 1, 0)])
+def test_quant_conv2d_matches_conv_on_dequantized_weight(fmt, g, cin, cout, k, stride, pad):
+    torch.manual_seed(cin + cout)
+    conv = torch.nn.Conv2d(cin, cout, k, stride=stride, padding=pad)
+    q = jq.JenksQuantConv2d(conv, 4, fmt=fmt, group_size=g).to(DEV)
+    x = torch.randn(2, cin, 9, 11).to(DEV)
+    y = q(x)
+    w_hat = q.dequantized_weight()
+    ref = torch.nn.functional.conv2d(x.double(), w_hat.double(), q.bias.double(), stride=stride, padding=pad).float()
+    assert y.shape == ref.shape
+    assert formats.rel_err(y.cpu().numpy(), ref.cpu().numpy()) <= TOL
+    q.commit()
+    assert q.hard_quant and torch.equal(q(x), y)
+
+
+def test_packed_checkpoint_model_runs_like_quantize_module():
+    from if_i_could_turn_back_time_b200 import checkpoint
+    torch.manual_seed(1)
+    model = torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(784, 300), torch.nn.ReLU(), torch.nn.Linear(300, 10))
+    spec = jq.QuantSpec("gf4", 0, 0)
+    packed = checkpoint.pack_state_dict(model.state_dict(), spec)
+    m1 = checkpoint.load_packed_into(torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(784, 300), torch.nn.ReLU(),
+                                                         torch.nn.Linear(300, 10)), packed).to(DEV)
+    m2 = jq.quantize_module(model, 4, fmt="gf4", group_size=0).to(DEV)
+    x = torch.rand(3, 1, 28, 28, device=DEV)
+    assert torch.equal(m1(x), m2(x))
+
+
+# ------------------------------------------------------------ GPU packer ----
+@pytest.mark.parametrize("N,K,g,had", [(64, 256, 32, 0), (33, 4096, 32, 128), (17, 1024, 128, 0), (5, 2048, 1024, 128)])
+def test_e2m1_gpu_packer_is_bit_identical_to_host_packer(N, K, g, had):
+    W = _weights(N, K, N * 3 + K)
+    W[0, :g] = 0
+    W[1, :32] = torch.tensor([6, 0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25, -0.75, -5.0, -6] + [0] * 20) * 0.01
+    spec = jq.QuantSpec("e2m1", g, had)
+    host = jq.pack_weight(W, spec)
+    dev = jq.pack_weight(W.to(DEV), spec)
+    assert dev.qweight.is_cuda
+    assert torch.equal(dev.qweight.cpu(), host.qweight)
+    assert torch.equal(dev.scales.cpu().view(torch.int16), host.scales.view(torch.int16))
+
+
 # ------------------------------------------------------ two-class Jenks ----
 @pytest.mark.parametrize("n", [1, 2, 7, 300, 2049, 235200])
 def test_two_class_jenks_break_matches_reference_form(n):
