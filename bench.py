@@ -133,7 +133,7 @@ def build_stack(name: str, rank: int, world: int, batch: int, device, threads: i
         W = torch.randn(N, K, generator=gen) * std     # every rank draws the same matrix, keeps its rows
         if fmt == "e2m1":
             W = W.bfloat16().float()
-        proto[label] = jq.pack_weight(W[lo:hi], spec, threads=threads)
+        proto[label] = jq.pack_weight(W[lo:hi].to(device), spec, threads=threads)   # quantised on the GPU
         del W
     pack_s = time.time() - t0
     weights, labels = [], []

@@ -53,6 +53,8 @@ _SIGNATURES = {
     "jq_jenks2_workspace_bytes": (c_size_t, [ctypes.c_longlong]),
     "jq_jenks2_break": (c_int, [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "jq_pack_e2m1": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "jq_pack_gf4_workspace_bytes": (c_size_t, [c_int]),
+    "jq_pack_gf4": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "jq_pack_e2m1_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
     "jq_pack_gf4_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int]),
     "jq_rotate_weights_host": (c_int, [c_void_p, c_int, c_int, c_int, c_int]),

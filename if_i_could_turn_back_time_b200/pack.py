@@ -67,6 +67,34 @@ def _pack_e2m1_cuda(W: torch.Tensor, spec: QuantSpec, rotate: bool) -> PackedWei
     return PackedWeight(spec, N, K, q, s, None)
 
 
+def _pack_gf4_cuda(W: torch.Tensor, spec: QuantSpec, rotate: bool) -> PackedWeight:
+    """GF4 quantisation on the GPU: one CTA per row runs the same exact
+    16-class Jenks dynamic programme as the host packer, bit for bit."""
+    import ctypes
+    lib = _lib.load()
+    from . import ops
+    Wf = W.detach().float().contiguous()
+    N, K = Wf.shape
+    g = spec.group_size
+    if g and K % g:
+        raise ValueError(f"K={K} is not a multiple of the group size {g}")
+    if spec.had_block and rotate:
+        if K % spec.had_block:
+            raise ValueError(f"K={K} is not a multiple of the rotation block {spec.had_block}")
+        Wf = ops.fwht_block(Wf, spec.had_block)
+    q = torch.zeros((N, row_stride_codes(K) // 2), dtype=torch.uint8, device=W.device)
+    s = torch.empty((N, K // g), dtype=torch.float16, device=W.device) if g else None
+    cb = torch.empty((N, 16), dtype=torch.float16, device=W.device)
+    P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
+    with torch.cuda.device(W.device):
+        wsb = lib.jq_pack_gf4_workspace_bytes(K)
+        ws = torch.empty(wsb, dtype=torch.uint8, device=W.device)
+        st = lib.jq_pack_gf4(P(Wf), N, K, g, P(q), P(s), P(cb), P(ws), wsb,
+                             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(st, "jq_pack_gf4")
+    return PackedWeight(spec, N, K, q, s, cb)
+
+
 def pack_weight(W: torch.Tensor, spec: QuantSpec, threads: int = 0, rotate: bool = True) -> PackedWeight:
     """Quantise and pack W [N, K].  With ``spec.had_block`` the weight is first
     multiplied on the right by the block Hadamard matrix (fp32), so that
@@ -74,6 +102,8 @@ def pack_weight(W: torch.Tensor, spec: QuantSpec, threads: int = 0, rotate: bool
     lib = _lib.load()
     if W.is_cuda and spec.fmt == "e2m1" and _gpu_packable(W, spec):
         return _pack_e2m1_cuda(W, spec, rotate)
+    if W.is_cuda and spec.fmt == "gf4" and W.shape[1] <= 51200:
+        return _pack_gf4_cuda(W, spec, rotate)
     Wf = W.detach().to("cpu", torch.float32).contiguous().clone()
     N, K = Wf.shape
     g = spec.group_size

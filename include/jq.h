@@ -231,6 +231,13 @@ int jq_jenks2_break(const float *sorted, long long n, double *var_or_null, doubl
 int jq_pack_e2m1(const float *W, int N, int K, int g, void *qweight, void *scales,
                  jq_stream_t stream);
 
+/* GF4 packer on the device (per-row 16-class Jenks natural breaks, one CTA per
+ * row), bit-identical to jq_pack_gf4_host; rows up to 51200 values.  scales
+ * may be NULL when g == 0.  workspace: jq_pack_gf4_workspace_bytes(K) bytes. */
+size_t jq_pack_gf4_workspace_bytes(int K);
+int jq_pack_gf4(const float *W, int N, int K, int g, void *qweight, void *scales_or_null,
+                void *codebook, void *workspace, size_t workspace_bytes, jq_stream_t stream);
+
 /* ---- host-side packers (CPU, multi-threaded; one-off, not the hot path) ----
  * Replace the grid/scale construction of QuantLinear.__init__
  * (Quantization_Experiments/layers.py:22-26) for the packed formats.  All

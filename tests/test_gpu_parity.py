@@ -363,6 +363,33 @@ def test_e2m1_gpu_packer_is_bit_identical_to_host_packer(N, K, g, had):
     assert torch.equal(dev.scales.cpu().view(torch.int16), host.scales.view(torch.int16))
 
 
+@pytest.mark.parametrize("N,K,g,had", [(24, 1024, 128, 0), (9, 4096, 128, 128), (5, 784, 0, 0), (7, 300, 0, 0),
+                                        (4, 11008, 128, 128), (3, 100, 0, 0)])
+def test_gf4_gpu_packer_is_bit_identical_to_host_packer(N, K, g, had):
+    W = _weights(N, K, N * 5 + K)
+    spec = jq.QuantSpec("gf4", g, had)
+    host = jq.pack_weight(W, spec)
+    dev = jq.pack_weight(W.to(DEV), spec)
+    assert torch.equal(dev.codebook.cpu().view(torch.int16), host.codebook.view(torch.int16))
+    assert torch.equal(dev.qweight.cpu(), host.qweight)
+    if g:
+        assert torch.equal(dev.scales.cpu().view(torch.int16), host.scales.view(torch.int16))
+
+
+def test_gf4_gpu_packer_ties_duplicates_and_sparse_rows():
+    g = torch.Generator("cpu").manual_seed(11)
+    cases = [torch.randint(-5, 6, (16, 256), generator=g).float(),
+             torch.round(torch.randn(16, 512, generator=g) * 8) / 8, torch.zeros(3, 64)]
+    sparse = torch.randn(10, 300, generator=g) * 0.1
+    sparse[torch.rand(10, 300, generator=g) < 0.95] = 0
+    cases.append(sparse)
+    for W in cases:
+        spec = jq.QuantSpec("gf4", 0, 0)
+        host, dev = jq.pack_weight(W, spec), jq.pack_weight(W.to(DEV), spec)
+        assert torch.equal(dev.codebook.cpu().view(torch.int16), host.codebook.view(torch.int16))
+        assert torch.equal(dev.qweight.cpu(), host.qweight)
+
+
 # ------------------------------------------------------ two-class Jenks ----
 @pytest.mark.parametrize("n", [1, 2, 7, 300, 2049, 235200])
 def test_two_class_jenks_break_matches_reference_form(n):
