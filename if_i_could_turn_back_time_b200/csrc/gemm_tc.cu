@@ -524,3 +524,40 @@ extern "C" int jq_tc_status(const void *workspace, jq_stream_t stream) {
     JQ_CUDA_TRY(cudaStreamSynchronize(st));
     return v;
 }
+
+// ---- bounded-wait self test ------------------------------------------------------
+// One CTA waits, with the same bounded wait the pipeline uses, on an mbarrier
+// that nothing ever arrives on.  The wait has to give up, raise the status
+// word and let the kernel return; the device stays usable.  (This is how the
+// failure path is exercised without faulting or hanging a GPU.)
+namespace jqtc {
+__global__ void __launch_bounds__(64) bounded_wait_selftest_kernel(int *status, uint32_t limit) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int s_err;
+    if (threadIdx.x == 0) {
+        s_err = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    volatile int *err = &s_err;
+    bool ok = true;
+    if (threadIdx.x == 32) {          // one waiter; nobody arrives
+        ok = false;
+        for (uint32_t i = 0; i < limit; ++i) {
+            if (mbar_try(smem_u32(&bar), 0)) { ok = true; break; }
+            if (i > 64) __nanosleep(64);
+        }
+        if (!ok) *err = JQ_ERR_TIMEOUT;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *status = s_err;
+}
+}  // namespace jqtc
+
+extern "C" int jq_selftest_bounded_wait(int *status_dev, unsigned int polls, jq_stream_t stream) {
+    if (!status_dev) return JQ_ERR_NULL_PTR;
+    if (polls == 0 || polls > (1u << 20)) return JQ_ERR_BAD_SHAPE;   // at most ~0.1 s of polling
+    jqtc::bounded_wait_selftest_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status_dev, polls);
+    return jq_launch_status();
+}

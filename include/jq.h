@@ -165,6 +165,14 @@ int jq_gemm_e2m1_tc(const void *qweight, const void *scales, const void *x,
  * check of Python_Jenks_Test/Jenks_Tests/cuda_helpers.py:205-208. */
 int jq_tc_status(const void *workspace, jq_stream_t stream);
 
+/* Self test of the failure path of the pipeline's device-side waits: one CTA
+ * polls (at most `polls` times, <= 2^20) an mbarrier that nothing arrives on,
+ * gives up, and writes JQ_ERR_TIMEOUT to *status_dev (device int).  Nothing
+ * traps or hangs; the context stays usable.  No reference counterpart (the
+ * reference's native code calls exit(1) on any CUDA error,
+ * CUDA_C_Code/include/layers.h:1195-1199). */
+int jq_selftest_bounded_wait(int *status_dev, unsigned int polls, jq_stream_t stream);
+
 /* One entry of a grouped launch: an independent GEMV problem. */
 typedef struct jq_problem {
     const void *qweight;

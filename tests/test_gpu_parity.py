@@ -267,6 +267,24 @@ def test_tensor_core_path_large_batch_is_split_and_matches_gemv():
     assert formats.rel_err(y_tc.cpu().numpy(), y_cc.cpu().numpy()) <= 1e-5  # both exact up to fp32 summation
 
 
+def test_bounded_wait_gives_up_with_a_status_and_the_device_stays_usable():
+    """Failure path of the pipeline's waits, exercised without a fault: a wait on a barrier that nothing
+    signals runs out after a bounded number of polls, the kernel reports JQ_ERR_TIMEOUT and returns."""
+    import ctypes
+    from if_i_could_turn_back_time_b200 import _lib
+    lib = _lib.load()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    st = lib.jq_selftest_bounded_wait(ctypes.c_void_p(status.data_ptr()), 4096,
+                                      ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == -7 and "wait" in _lib.strerror(-7)
+    # the context is still healthy: a normal call right after works
+    pw = jq.pack_weight(_weights(64, 256, 1), jq.QuantSpec("e2m1", 32, 0)).to(DEV)
+    assert torch.isfinite(ops.linear(torch.randn(16, 256, device=DEV).bfloat16(), pw).float()).all()
+    assert ops.tc_status() == 0
+
+
 # ---------------------------------------------------------------- grouped ----
 @pytest.mark.parametrize("fmt,g,had,B", [("gf4", 128, 128, 1), ("e2m1", 32, 0, 2), ("gf4", 128, 128, 4)])
 def test_grouped_launch_equals_single_launches(fmt, g, had, B):
