@@ -26,21 +26,43 @@ namespace jqtc {
 #ifndef JQ_TC_X
 #define JQ_TC_X 0   // timing experiments only: 1 = no MMAs, 2 = no weight copies, 4 = no epilogue reads
 #endif
-constexpr int kThreads = 384;   // 4 service warps + 8 epilogue warps
+#ifdef JQ_TC_TRACE
+__device__ unsigned long long g_trace[8 * 256];   // [event][stage iteration] SM clock of CTA 0
+__device__ __forceinline__ void trace(int ev, uint32_t it) {
+    if (blockIdx.x == 0 && it < 256) { g_trace[ev * 256 + it] = (unsigned long long)clock64(); }
+}
+#define TRACE(ev, it) trace(ev, it)
+#else
+#define TRACE(ev, it)
+#endif
+#ifndef JQ_TC_PREFETCH
+#define JQ_TC_PREFETCH 12
+#endif
+constexpr int kPrefetch = JQ_TC_PREFETCH;   // stages of weights requested into L2 ahead of the shared-memory ring
+constexpr int kThreads = 512;   // warps 0-3 producers, 4-7 MMA issuers (4 owns tensor memory), 8-15 epilogue
+constexpr int kMmaWarps = 2;   // issuer w owns accumulator buffer w and the stages it = w, w+2, ... (warps 6, 7 idle)   // 4 service warps + 8 epilogue warps
 constexpr int kTileM = 128;
 constexpr int kHeaderBytes = 512;      // workspace: int status, int exponent[64]
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 template <int BN, int TERMS>
 struct Cfg {
-    static constexpr int G = (256 / BN) < 8 ? (256 / BN) : 8;  // 32-code groups per stage = accumulators per buffer
+    static constexpr int G = (256 / BN) < 8 ? (256 / BN) : 8;  // 32-code groups per shared-memory stage
     static constexpr int SK = G * 32;                          // codes of K per stage
     // padded FP4: 16 codes per 16-byte chunk; one chunk column = 128 rows x 16 B, plus 16 B so that the 16
     // lanes that copy one row's 16 chunks do not all hit the same shared-memory bank
     static constexpr int A_CHUNK = kTileM * 16 + 16;
     static constexpr int A_BYTES = 2 * G * A_CHUNK;
-    static constexpr int B_BYTES = TERMS * G * 2 * BN * 16;    // [term][group][chunk][column][16 B]
-    static constexpr int ACC_COLS = G * BN;                    // fp32 accumulator columns per buffer (<= 256)
+    // The issue rate of tcgen05.mma from one thread (~70 clk each, whatever N is) bounds the kernel, so as
+    // few MMAs per group as possible: while TERMS x BN <= 64 columns the E4M3 terms sit side by side in N
+    // (one MMA per group, the epilogue adds the term columns); beyond that they extend K (TERMS MMAs).
+    static constexpr int TN = (TERMS * BN <= 64) ? TERMS : 1;  // terms laid out along N
+    static constexpr int TK = TERMS / TN;                      // terms accumulated along K
+    static constexpr int NW = TN * BN;                         // MMA N
+    static constexpr int B_BYTES = G * TK * 2 * NW * 16;       // [group][k-term][chunk][n-term * BN + column][16 B]
+    static constexpr int GA_ = 256 / NW;                       // groups whose accumulators fit one 256-column buffer
+    static constexpr int GA = GA_ >= G ? G : (GA_ >= 4 ? 4 : (GA_ >= 2 ? 2 : 1));
+    static constexpr int ROUNDS = G / GA;                      // accumulator rounds per stage
     static constexpr int TMEM_COLS = 512;
 };
 
@@ -69,12 +91,17 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: false (and the CTA-wide error flag raised) when it gives up.
+// Bounded wait: false (and the CTA-wide error flag raised) when it gives up, after kSpinLimit polls or
+// ~0.25 s of SM clock, whichever comes first.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *err) {
+    const long long t0 = clock64();
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try(bar, parity)) return true;
         if (*err) return false;
-        if (i > 8192) __nanosleep(64);  // back off only when the wait is clearly long: a sleeping waiter wakes late
+        if (i > 8192) {
+            __nanosleep(64);  // back off only when the wait is clearly long: a sleeping waiter wakes late
+            if (clock64() - t0 > 500000000LL) break;
+        }
     }
     *err = JQ_ERR_TIMEOUT;
     return false;
@@ -151,8 +178,8 @@ __device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.syn
 // ---- activation preparation -----------------------------------------------------
 // x[B,K] -> (rotate) -> u = x * 2^-e with max|u| < 256 -> t1 = e4m3(u),
 // t2 = e4m3(u - t1), t3 = e4m3(u - t1 - t2) -> bytes in the smem-ready layout
-// [stage][term][group][chunk][column][16].  Columns >= B are zero.  One block
-// per column.
+// [stage][group][k-term][chunk][n-term * BN + column][16] (see Cfg).  Columns >= B
+// are zero.  One block per column.
 __device__ __forceinline__ int tc_exponent(float amax, bool had) {
     uint32_t bits = __float_as_uint(amax);
     int field = (bits >> 23) & 0xff;
@@ -171,7 +198,8 @@ __device__ __forceinline__ float e4m3_round(float v, uint8_t &byte) {
 template <int BN, int TERMS>
 __global__ void __launch_bounds__(256) tc_prepare_kernel(const void *__restrict__ x, int B, int K, int had, int x_dtype,
                                                           unsigned char *__restrict__ ws) {
-    constexpr int G = Cfg<BN, TERMS>::G, SK = Cfg<BN, TERMS>::SK;
+    using C = Cfg<BN, TERMS>;
+    constexpr int G = C::G, SK = C::SK;
     __shared__ float sred[8];
     __shared__ int sexp;
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -218,7 +246,8 @@ __global__ void __launch_bounds__(256) tc_prepare_kernel(const void *__restrict_
         const int st = k0 / SK, kk = k0 % SK, g = kk >> 5, ch = (kk >> 4) & 1, off = kk & 15;
 #pragma unroll
         for (int t = 0; t < TERMS; ++t) {
-            const size_t idx = ((((size_t)(st * TERMS + t) * G + g) * 2 + ch) * BN + b) * 16 + off;
+            const int tk = t / C::TN, tn = t % C::TN;
+            const size_t idx = (((((size_t)st * G + g) * C::TK + tk) * 2 + ch) * C::NW + tn * BN + b) * 16 + off;
             *reinterpret_cast<uint32_t *>(xq + idx) = packed[t];
         }
     }
@@ -239,7 +268,7 @@ struct TcArgs {
 template <int BN, int TERMS>
 __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
     using C = Cfg<BN, TERMS>;
-    constexpr int G = C::G, SK = C::SK, S = stages<BN, TERMS>();
+    constexpr int G = C::G, SK = C::SK, S = stages<BN, TERMS>(), NW = C::NW, GA = C::GA, ROUNDS = C::ROUNDS, TK = C::TK, TN = C::TN;
     constexpr int A_BYTES = C::A_BYTES, B_BYTES = C::B_BYTES, STAGE = stage_bytes<BN, TERMS>();
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t bars[2 * 6 + 4];
@@ -255,8 +284,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
     if (tid == 0) {
         s_err = 0;
         for (int s = 0; s < S; ++s) {
-            mbar_init(full0 + 8 * s, 96);   // 32 lanes of each of the 3 producer warps, arriving through cp.async completion
-            mbar_init(empty0 + 8 * s, 9);   // one tcgen05.commit + the 8 epilogue warps (they read the scale tile)
+            mbar_init(full0 + 8 * s, 128);  // 32 lanes of each of the 4 producer warps, arriving through cp.async completion
+            mbar_init(empty0 + 8 * s, 8);   // the 8 epilogue warps, once the stage's last accumulator round is complete
+                                            // (that implies its MMAs have read the stage; the warps have read the scales)
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(tfull0 + 8 * i, 1);   // one tcgen05.commit
@@ -267,7 +297,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
     // the upper 8 bytes of every FP4 chunk are padding that no copy writes: keep them defined
     for (uint32_t i = tid; i < (uint32_t)(S * STAGE) / 16; i += kThreads)
         asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(smem_base + i * 16), "r"(0u) : "memory");
-    if (warp == 3) {
+    if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(C::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -283,84 +313,102 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
     const int ngroups = a.K >> 5;
     const unsigned char *xq = a.ws + kHeaderBytes;
 
-    if (warp < 2) {
-        // ---- weight producers: two warps, 64 rows each.  16 lanes copy the 16 chunks (8 B) of one row's
-        //      stage slice, so global reads coalesce; two rows per instruction.
+    if (warp < 4) {
+        // ---- producers, four warps of 32 weight rows each.  16 lanes copy the 16 chunks (8 B) of one row's
+        //      stage slice, so global reads coalesce; two rows per instruction.  Each warp also copies a
+        //      quarter of the activation tile and its rows' group scales.
         uint32_t it = 0;
         const int c = lane & 15, rsub = lane >> 4;
         for (int item = blockIdx.x; item < nitems && !*err; item += gridDim.x) {
             const int tile = item / a.kparts, part = item % a.kparts;
+            const bool full_tile = tile * kTileM + kTileM <= a.N;
             for (int st = 0; st < nst; ++st, ++it) {
                 const int s = it % S;
                 if (!mbar_wait(empty0 + 8 * s, ((it / S) & 1) ^ 1, err)) break;
-                const uint32_t dstA = smem_base + s * STAGE + c * C::A_CHUNK;
+                if (warp == 0 && lane == 0) TRACE(0, it);
+                const uint32_t sa = smem_base + s * STAGE;
+                uint32_t dst = sa + c * C::A_CHUNK + (warp * 32 + rsub) * 16;
                 const size_t koff = (size_t)(part * nst + st) * (SK / 2) + c * 8;
                 if (c < 2 * G && !(JQ_TC_X & 2)) {
+                    if (full_tile) {
+                        const uint8_t *src = a.qw + (size_t)(tile * kTileM + warp * 32 + rsub) * ldw + koff;
+                        const size_t step = (size_t)2 * ldw;
 #pragma unroll 8
-                    for (int rr = 0; rr < 32; ++rr) {
-                        const int r = warp * 64 + rr * 2 + rsub;
-                        const int row = min(tile * kTileM + r, a.N - 1);
-                        cp_async8(dstA + r * 16, a.qw + (size_t)row * ldw + koff);
-                    }
-                }
-                cp_async_arrive(full0 + 8 * s);
-            }
-        }
-    } else if (warp == 2) {
-        // ---- activation + scale producer: the stage's activation tile is one contiguous block of the prepared buffer
-        uint32_t it = 0;
-        for (int item = blockIdx.x; item < nitems && !*err; item += gridDim.x) {
-            const int tile = item / a.kparts, part = item % a.kparts;
-            for (int st = 0; st < nst; ++st, ++it) {
-                const int s = it % S;
-                if (!mbar_wait(empty0 + 8 * s, ((it / S) & 1) ^ 1, err)) break;
-                const uint32_t dstB = smem_base + s * STAGE + A_BYTES;
-                const unsigned char *src = xq + (size_t)(part * nst + st) * B_BYTES;
-                for (int i = lane; i < B_BYTES / 16; i += 32) cp_async16(dstB + i * 16, src + (size_t)i * 16);
-                // the tile's group scales: G fp16 per row, to 16 bytes per row
-#pragma unroll
-                for (int rr = 0; rr < 4; ++rr) {
-                    const int r = rr * 32 + lane;
-                    const int row = min(tile * kTileM + r, a.N - 1);
-                    const __half *sp = a.scales + (size_t)row * ngroups + (size_t)(part * nst + st) * G;
-                    if (G == 8) cp_async16(dstB + B_BYTES + r * 16, sp);
-                    else cp_async8(dstB + B_BYTES + r * 16, sp);
-                }
-                cp_async_arrive(full0 + 8 * s);
-            }
-        }
-    } else if (warp == 3) {
-        // ---- MMA issuer (one thread): per 32-code group, TERMS MMAs (K = 32 each) into the group's accumulator
-        if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc(kTileM, BN);
-            uint32_t it = 0;
-            for (int item = blockIdx.x; item < nitems && !*err; item += gridDim.x) {
-                for (int st = 0; st < nst; ++st, ++it) {
-                    const int s = it % S, ab = it & 1;
-                    if (!mbar_wait(tempty0 + 8 * ab, ((it >> 1) & 1) ^ 1, err)) break;  // accumulator buffer drained
-                    if (!mbar_wait(full0 + 8 * s, (it / S) & 1, err)) break;            // tiles landed
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    tc_fence_after();
-                    const uint32_t sa = smem_base + s * STAGE, sb = sa + A_BYTES;
-#pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        const uint64_t ad = smem_desc(sa + g * (2 * C::A_CHUNK), C::A_CHUNK, 128);
-#pragma unroll
-                        for (int t = 0; t < TERMS; ++t) {
-                            const uint64_t bd = smem_desc(sb + (t * G + g) * (2 * BN * 16), BN * 16, 128);
-                            if (!(JQ_TC_X & 1)) mma_f8f6f4(tmem + ab * 256 + g * BN, ad, bd, idesc, t > 0 ? 1u : 0u);
+                        for (int rr = 0; rr < 16; ++rr) { cp_async8(dst, src); dst += 32; src += step; }
+                    } else {
+#pragma unroll 4
+                        for (int rr = 0; rr < 16; ++rr) {
+                            const int row = min(tile * kTileM + warp * 32 + rr * 2 + rsub, a.N - 1);
+                            cp_async8(dst, a.qw + (size_t)row * ldw + koff);
+                            dst += 32;
                         }
                     }
-                    mma_commit(empty0 + 8 * s);    // smem stage reusable once these MMAs have read it
-                    mma_commit(tfull0 + 8 * ab);   // accumulators of this stage complete
+                }
+                // a quarter of the stage's activation tile (one contiguous block of the prepared buffer)
+                {
+                    const unsigned char *src = xq + (size_t)(part * nst + st) * B_BYTES;
+                    for (int i = warp * 32 + lane; i < B_BYTES / 16; i += 128) cp_async16(sa + A_BYTES + i * 16, src + (size_t)i * 16);
+                }
+                // this warp's 32 rows' group scales: G fp16 per row, to 16 bytes per row
+                {
+                    const int r = warp * 32 + lane;
+                    const int row = min(tile * kTileM + r, a.N - 1);
+                    const __half *sp = a.scales + (size_t)row * ngroups + (size_t)(part * nst + st) * G;
+                    if (G == 8) cp_async16(sa + A_BYTES + B_BYTES + r * 16, sp);
+                    else cp_async8(sa + A_BYTES + B_BYTES + r * 16, sp);
+                }
+                cp_async_arrive(full0 + 8 * s);
+                if (warp == 0 && lane == 0) TRACE(1, it);
+            }
+        }
+    } else if (warp < 4 + kMmaWarps) {
+        // ---- MMA issuers: one thread in each of four warps; issuer w takes the stages it = w, w+4, ...
+        //      Per stage an issuer spends ~0.7 us in serial latencies (two mbarrier waits, the tcgen05.mma
+        //      issue itself at ~100 clk per instruction whatever its size, the commit); four issuers working on
+        //      different stages overlap them.  Accumulator buffers and barrier phases follow the global stage
+        //      and round counters, so the issuers need no ordering among themselves.
+        const int w = warp - 4;
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(kTileM, NW);
+            uint32_t it = 0;
+            for (int item = blockIdx.x; item < nitems && !*err; item += gridDim.x) {
+                for (int st = 0; st < nst && !*err; ++st, ++it) {
+                    if ((int)(it % kMmaWarps) != w) continue;
+                    const int s = it % S;
+                    const int ab = it & 1;                 // == w: this issuer's accumulator buffer
+                    uint32_t pa = (it >> 1) * ROUNDS;      // rounds this buffer has seen so far
+                    if (!mbar_wait(full0 + 8 * s, (it / S) & 1, err)) break;            // tiles landed
+                    if (w == 0) TRACE(3, it);
+#ifdef JQ_TC_PROXY_FENCE
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
+                    const uint32_t sa = smem_base + s * STAGE, sb = sa + A_BYTES;
+#pragma unroll
+                    for (int rd = 0; rd < ROUNDS; ++rd, ++pa) {
+                        if (!mbar_wait(tempty0 + 8 * ab, (pa & 1) ^ 1, err)) break;  // accumulator buffer drained
+                        tc_fence_after();
+                        if (w == 0 && rd == 0) TRACE(2, it);
+#pragma unroll
+                        for (int gg = 0; gg < GA; ++gg) {
+                            const int g = rd * GA + gg;
+                            const uint64_t ad = smem_desc(sa + g * (2 * C::A_CHUNK), C::A_CHUNK, 128);
+#pragma unroll
+                            for (int tk = 0; tk < TK; ++tk) {
+                                const uint64_t bd = smem_desc(sb + (g * TK + tk) * (2 * NW * 16), NW * 16, 128);
+                                if (!(JQ_TC_X & 1)) mma_f8f6f4(tmem + ab * 256 + gg * NW, ad, bd, idesc, tk > 0 ? 1u : 0u);
+                            }
+                        }
+                        mma_commit(tfull0 + 8 * ab);   // this round's accumulators complete
+                    }
+                    if (w == 0) TRACE(4, it);
                 }
             }
         }
-    } else {
+    } else if (warp >= 8) {
         // ---- epilogue, 8 warps: thread = one accumulator lane (weight row) x one half of the batch columns.
         //      The read of group g+1 from tensor memory is in flight while group g is scaled and added.
         const int q = warp & 3;                // tensor-memory lane quarter this warp may touch
-        const int h = (warp - 4) >> 2;         // which half of the columns
+        const int h = (warp - 8) >> 2;         // which half of the columns
         constexpr int CH = BN / 2;
         const int r = q * 32 + lane;
         const int *hdr = reinterpret_cast<const int *>(a.ws);
@@ -372,37 +420,56 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
 #pragma unroll
             for (int b = 0; b < CH; ++b) acc[b] = 0.f;
             bool ok = true;
-            for (int st = 0; st < nst; ++st, ++it) {
-                const int s = it % S, ab = it & 1;
-                ok = __all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * ab, (it >> 1) & 1, err));  // warp-uniform outcome
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + ab * 256 + h * CH;
-                uint32_t d[2][CH];
-                tmem_ld<CH>(tbase, d[0]);
+            for (int st = 0; st < nst && ok; ++st, ++it) {
+                const int s = it % S, ab = it & 1;     // the stage's accumulator buffer (its issuer's)
+                uint32_t pa = (it >> 1) * ROUNDS;
                 float sc[G];  // this row's G scales of the stage, staged in shared memory by the producer
-                {
-                    const uint32_t sp = smem_base + s * STAGE + A_BYTES + B_BYTES + r * 16;
-                    uint32_t w[4];
-                    if (G == 8) asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(sp));
-                    else asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(sp));
 #pragma unroll
-                    for (int g = 0; g < G; ++g)
-                        sc[g] = __half2float(__ushort_as_half((uint16_t)((g & 1) ? (w[g >> 1] >> 16) : (w[g >> 1] & 0xffffu))));
+                for (int rd = 0; rd < ROUNDS; ++rd, ++pa) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * ab, pa & 1, err));  // warp-uniform outcome
+                    if (!ok) break;
+                    if (warp == 8 && lane == 0 && rd == 0) TRACE(5, it);
+                    tc_fence_after();
+                    const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + ab * 256 + h * CH;
+                    uint32_t d[2][TN][CH];
+#pragma unroll
+                    for (int tn = 0; tn < TN; ++tn) tmem_ld<CH>(tbase + tn * BN, d[0][tn]);
+                    if (rd == 0) {
+                        // tfull of the first round implies the stage's copies have landed (the MMA thread saw 'full')
+                        const uint32_t sp = smem_base + s * STAGE + A_BYTES + B_BYTES + r * 16;
+                        uint32_t w[4];
+                        if (G == 8) asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(sp));
+                        else asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(sp));
+#pragma unroll
+                        for (int g = 0; g < G; ++g)
+                            sc[g] = __half2float(__ushort_as_half((uint16_t)((g & 1) ? (w[g >> 1] >> 16) : (w[g >> 1] & 0xffffu))));
+                    }
+                    if (rd == ROUNDS - 1) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(empty0 + 8 * s);  // all MMAs of the stage are done and its scales are in registers
+                    }
+                    tmem_wait();
+#pragma unroll
+                    for (int gg = 0; gg < ((JQ_TC_X & 4) ? 1 : GA); ++gg) {
+                        if (gg + 1 < GA) {
+#pragma unroll
+                            for (int tn = 0; tn < TN; ++tn) tmem_ld<CH>(tbase + (gg + 1) * NW + tn * BN, d[(gg + 1) & 1][tn]);
+                        }
+                        const float sg = sc[rd * GA + gg];
+#pragma unroll
+                        for (int i = 0; i < CH; ++i) {
+                            float v = __uint_as_float(d[gg & 1][0][i]);
+#pragma unroll
+                            for (int tn = 1; tn < TN; ++tn) v += __uint_as_float(d[gg & 1][tn][i]);
+                            acc[i] = fmaf(v, sg, acc[i]);
+                        }
+                        if (gg + 1 < GA) tmem_wait();
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty0 + 8 * ab);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(empty0 + 8 * s);  // scale tile consumed
-                tmem_wait();
-#pragma unroll
-                for (int g = 0; g < ((JQ_TC_X & 4) ? 1 : G); ++g) {
-                    if (g + 1 < G) tmem_ld<CH>(tbase + (g + 1) * BN, d[(g + 1) & 1]);
-#pragma unroll
-                    for (int i = 0; i < CH; ++i) acc[i] = fmaf(__uint_as_float(d[g & 1][i]), sc[g], acc[i]);
-                    if (g + 1 < G) tmem_wait();
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tempty0 + 8 * ab);
+                if (warp == 8 && lane == 0) TRACE(6, it);
             }
             if (!ok) break;
             if (row < a.N) {
@@ -426,7 +493,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
     tc_fence_before();
     __syncthreads();
     if (tid == 0 && s_err) atomicExch(reinterpret_cast<int *>(a.ws), s_err);
-    if (warp == 3) {
+    if (warp == 4) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::TMEM_COLS) : "memory");
     }
@@ -561,3 +628,9 @@ extern "C" int jq_selftest_bounded_wait(int *status_dev, unsigned int polls, jq_
     jqtc::bounded_wait_selftest_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status_dev, polls);
     return jq_launch_status();
 }
+
+#ifdef JQ_TC_TRACE
+extern "C" int jq_tc_trace_read(unsigned long long *host_out) {
+    return cudaMemcpyFromSymbol(host_out, jqtc::g_trace, sizeof(unsigned long long) * 8 * 256) == cudaSuccess ? 0 : -1;
+}
+#endif
