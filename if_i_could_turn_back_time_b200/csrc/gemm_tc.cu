@@ -47,16 +47,19 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 
 template <int BN, int TERMS>
 struct Cfg {
-    static constexpr int G = (256 / BN) < 8 ? (256 / BN) : 8;  // 32-code groups per shared-memory stage
+#ifndef JQ_TC_G64
+#define JQ_TC_G64 8
+#endif
+    static constexpr int G = BN >= 64 ? JQ_TC_G64 : 8;         // 32-code groups per shared-memory stage
     static constexpr int SK = G * 32;                          // codes of K per stage
     // padded FP4: 16 codes per 16-byte chunk; one chunk column = 128 rows x 16 B, plus 16 B so that the 16
     // lanes that copy one row's 16 chunks do not all hit the same shared-memory bank
     static constexpr int A_CHUNK = kTileM * 16 + 16;
     static constexpr int A_BYTES = 2 * G * A_CHUNK;
     // The issue rate of tcgen05.mma from one thread (~70 clk each, whatever N is) bounds the kernel, so as
-    // few MMAs per group as possible: while TERMS x BN <= 64 columns the E4M3 terms sit side by side in N
+    // few MMAs per group as possible: while TERMS x BN <= 48 columns the E4M3 terms sit side by side in N
     // (one MMA per group, the epilogue adds the term columns); beyond that they extend K (TERMS MMAs).
-    static constexpr int TN = (TERMS * BN <= 64) ? TERMS : 1;  // terms laid out along N
+    static constexpr int TN = (TERMS * BN <= 48) ? TERMS : 1;  // terms laid out along N
     static constexpr int TK = TERMS / TN;                      // terms accumulated along K
     static constexpr int NW = TN * BN;                         // MMA N
     static constexpr int B_BYTES = G * TK * 2 * NW * 16;       // [group][k-term][chunk][n-term * BN + column][16 B]
@@ -579,6 +582,22 @@ extern "C" int jq_gemm_e2m1_tc(const void *qweight, const void *scales, const vo
     if (bn == 16) return terms == 2 ? launch_tc<16, 2>(a, x, had_block, x_dtype, st) : launch_tc<16, 3>(a, x, had_block, x_dtype, st);
     if (bn == 32) return terms == 2 ? launch_tc<32, 2>(a, x, had_block, x_dtype, st) : launch_tc<32, 3>(a, x, had_block, x_dtype, st);
     return terms == 2 ? launch_tc<64, 2>(a, x, had_block, x_dtype, st) : launch_tc<64, 3>(a, x, had_block, x_dtype, st);
+}
+
+// A decode step's worth of batched layers in one host call: the launches of every problem are enqueued
+// back to back on the stream, sharing one workspace (stream order keeps them apart).
+extern "C" int jq_gemm_e2m1_tc_multi(const jq_problem *problems_host, int n, int B, int x_dtype, int y_dtype,
+                                     void *workspace, size_t workspace_bytes, jq_stream_t stream) {
+    if (!problems_host || !workspace) return JQ_ERR_NULL_PTR;
+    if (n <= 0) return JQ_ERR_BAD_SHAPE;
+    for (int i = 0; i < n; ++i) {
+        const jq_problem &p = problems_host[i];
+        if (p.ldy != 0 && p.ldy != p.N) return JQ_ERR_UNSUPPORTED;
+        int st = jq_gemm_e2m1_tc(p.qweight, p.scales, p.x, p.bias, p.y, p.N, p.K, B, p.g, p.had_block, x_dtype, y_dtype,
+                                 workspace, workspace_bytes, stream);
+        if (st) return st;
+    }
+    return JQ_OK;
 }
 
 // Status word of the last jq_gemm_e2m1_tc call that used this workspace

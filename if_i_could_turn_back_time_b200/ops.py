@@ -290,6 +290,20 @@ class GroupedGemv:
                 _lib.check(st, "jq_gemv_grouped_peers")
             # batch x K too large for one staged activation per CTA: one (split-K) launch per matrix instead
             self._per_problem = True
+        w0 = self.weights[0]
+        if (self.batch <= MAX_TC_BATCH and not any(self.row_offsets)
+                and all(tc_eligible(w.spec.fmt_id, w.K, w.spec.group_size, self.batch) for w in self.weights)):
+            # every matrix goes to the tensor-core kernel: one host call enqueues them all
+            global _last_tc_workspace
+            wsb = max(lib.jq_workspace_bytes(1, w.N, w.K, self.batch) for w in self.weights)
+            ws = _workspace(self.device, wsb)
+            with torch.cuda.device(self.device):
+                st = lib.jq_gemm_e2m1_tc_multi(ctypes.byref(self._problems_host), len(self.weights), self.batch,
+                                               _DT[self.x_dtype], _DT[self.x_dtype], _ptr(ws), ws.numel(), _stream())
+            _lib.check(st, "jq_gemm_e2m1_tc_multi")
+            _last_tc_workspace = ws
+            self.launches_per_run = None
+            return
         for w, x, y, b, nf, ro in zip(self.weights, self.xs, self.ys, self.biases, self.full_rows, self.row_offsets):
             y[:, ro:ro + w.N].copy_(linear(x, w, b))
         self.launches_per_run = None

@@ -219,6 +219,14 @@ int jq_gemv_grouped_peers(const jq_problem *problems_dev, const void *plan_host,
                           const void *plan_dev, int x_dtype, int y_dtype, int npeer,
                           const int64_t *peer_delta, jq_stream_t stream);
 
+/* n batched layers in one host call (problems_host is a HOST array whose
+ * pointers are device pointers; ldy must be 0 or N): the launches are enqueued
+ * back to back and share the workspace, which must be large enough for the
+ * largest problem.  Same reference counterpart as jq_gemm_e2m1_tc. */
+int jq_gemm_e2m1_tc_multi(const jq_problem *problems_host, int n, int B, int x_dtype,
+                          int y_dtype, void *workspace, size_t workspace_bytes,
+                          jq_stream_t stream);
+
 /* Bytes of caller-provided device scratch an op needs for these sizes. */
 size_t jq_workspace_bytes(int op, int N, int K, int B);
 

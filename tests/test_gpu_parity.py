@@ -285,6 +285,19 @@ def test_bounded_wait_gives_up_with_a_status_and_the_device_stays_usable():
     assert ops.tc_status() == 0
 
 
+def test_grouped_batched_layers_use_one_tensor_core_host_call():
+    shapes = [(512, 1024), (96, 2048), (300, 256)]
+    pws = [jq.pack_weight(_weights(n, k, n + k), jq.QuantSpec("e2m1", 32, 0)).to(DEV) for n, k in shapes]
+    grp = ops.GroupedGemv(pws, 24, torch.bfloat16)
+    gen = torch.Generator("cpu").manual_seed(5)
+    for x in grp.xs:
+        x.copy_(torch.randn(x.shape, generator=gen).bfloat16())
+    grp.run()
+    assert ops.tc_status() == 0
+    for pw, x, y in zip(pws, grp.xs, grp.ys):
+        assert torch.equal(y, ops.linear(x, pw))
+
+
 # ---------------------------------------------------------------- grouped ----
 @pytest.mark.parametrize("fmt,g,had,B", [("gf4", 128, 128, 1), ("e2m1", 32, 0, 2), ("gf4", 128, 128, 4)])
 def test_grouped_launch_equals_single_launches(fmt, g, had, B):
