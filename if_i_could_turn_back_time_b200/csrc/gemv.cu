@@ -137,6 +137,13 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void *src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
+// src_bytes < size: the rest of the destination is filled with zeros (0 = nothing is read)
+__device__ __forceinline__ void cp_async16_z(uint32_t dst, const void *src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4_z(uint32_t dst, const void *src, uint32_t src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -195,19 +202,21 @@ __device__ __forceinline__ void dot8_h2(const uint32_t (&h)[4], const uint4 &x, 
         : "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]), "r"(x.x), "r"(x.y), "r"(x.z), "r"(x.w));
 }
 
-// Eight GF4 codes times B x eight activations.  Each nibble, doubled, is OR-ed
-// into the 32-byte-aligned shared address of the row's 16-entry fp16 table
-// (one shift + one LOP3), looked up with a 16-bit shared load, and fed to the
-// mixed-precision FMA as a 16-bit register (no repacking).
+// Eight GF4 codes times B x eight activations.  The row's 16-entry fp16 table
+// sits at byte offset rb (a multiple of 32 below 256) of a 256-byte aligned
+// block tb of shared memory, so a lookup address is tb with its low byte
+// replaced by rb | 2 * nibble: two shifts and two LOP3 put the eight doubled
+// nibbles (OR-ed with rb) into the bytes of two registers, one PRMT per code
+// splices a byte into the address, a 16-bit shared load fetches the entry,
+// and it feeds the mixed-precision FMA as a 16-bit register (no repacking).
 template <int B>
-__device__ __forceinline__ void dot8_gf4(uint32_t word, uint32_t tb, const uint4 (&x)[B], float (&part)[B][2]) {
+__device__ __forceinline__ void dot8_gf4(uint32_t word, uint32_t tb, uint32_t rb4, const uint4 (&x)[B], float (&part)[B][2]) {
+    uint32_t m0, m1;  // bytes: 2 * nibbles {0,2,4,6} | rb  and  2 * nibbles {1,3,5,7} | rb
+    asm("lop3.b32 %0, %1, 0x1e1e1e1e, %2, 0xea;" : "=r"(m0) : "r"(word << 1), "r"(rb4));  // (a & b) | c
+    asm("lop3.b32 %0, %1, 0x1e1e1e1e, %2, 0xea;" : "=r"(m1) : "r"(word >> 3), "r"(rb4));
 #pragma unroll
     for (int bb = 0; bb < 4; ++bb) {
-        const uint32_t s0 = bb == 0 ? (word << 1) : (word >> (8 * bb - 1));
-        const uint32_t s1 = word >> (8 * bb + 3);
-        uint32_t o0, o1;
-        asm("lop3.b32 %0, %1, 0x1e, %2, 0xea;" : "=r"(o0) : "r"(s0), "r"(tb));  // (a & b) | c
-        asm("lop3.b32 %0, %1, 0x1e, %2, 0xea;" : "=r"(o1) : "r"(s1), "r"(tb));
+        const uint32_t o0 = __byte_perm(m0, tb, 0x7650 + bb), o1 = __byte_perm(m1, tb, 0x7650 + bb);
         uint16_t w0, w1;
         asm volatile("ld.shared.u16 %0, [%1];" : "=h"(w0) : "r"(o0));
         asm volatile("ld.shared.u16 %0, [%1];" : "=h"(w1) : "r"(o1));
@@ -228,7 +237,7 @@ struct Ring {
     static constexpr int kSlots = DEPTH * T;                   // 16-byte slots per thread
     static constexpr int kWBytes = kSlots * kThreads * 16;     // weight ring
     static constexpr int kSBytes = kSlots * kThreads * 4;      // scale-pair ring
-    static constexpr int kTabBytes = kWarps * DEPTH * T * 32 + 32;  // GF4 codebooks per warp and row group (+ alignment slack)
+    static constexpr int kTabBytes = kWarps * DEPTH * 256 + 256;  // GF4 codebooks: a 256-byte aligned block per warp and row group
     static constexpr int kBytes = kWBytes + kSBytes + kTabBytes;
 };
 
@@ -237,7 +246,18 @@ struct Ring {
 // Everything that is constant over a row group (row pointers, scale-pair
 // parity) is computed once per row group, so that a stage costs little beyond
 // its copies, its shared loads and the dot products themselves.
-template <int FMT, int B, int DEPTH>
+// FAST (the caller checked fast_scales(p)): group scales exist and are fetched
+// as aligned fp16 pairs by cp.async; the ragged end of a row is handled by
+// zero-filling copies instead of branches (zero codes and zero scales times
+// the zero-padded activation add nothing), so a stage has no data-dependent
+// control flow.
+__device__ __forceinline__ bool fast_scales(const GemvProblem &p) {
+    const int gq = p.g >> 5;
+    return p.g && (gq & (gq - 1)) == 0 && p.g <= 512 && (((size_t)p.N * p.lds) & 1) == 0 &&
+           (reinterpret_cast<uintptr_t>(p.scales) & 3u) == 0;
+}
+
+template <int FMT, int B, int DEPTH, bool FAST>
 __device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __half *xs, const int *sexp,
                          unsigned char *ring_base, int y_dtype) {
     using R_ = Ring<FMT, B, DEPTH>;
@@ -255,14 +275,14 @@ __device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __hal
     // lane's scale.  Needs a power-of-two group of at most 512 codes (so the
     // pair pointer advances by a constant, 4-byte-multiple step per stage), an
     // even element count (the pair never crosses the end) and an aligned base.
-    const bool scale_async = p.g && gpow2 && p.g <= 512 && (((size_t)N * ngroups) & 1) == 0 &&
-                             (reinterpret_cast<uintptr_t>(p.scales) & 3u) == 0;
+    const bool scale_async = FAST || (p.g && gpow2 && p.g <= 512 && (((size_t)N * ngroups) & 1) == 0 &&
+                                      (reinterpret_cast<uintptr_t>(p.scales) & 3u) == 0);
     const int sadv = scale_async ? (2048 / p.g) : 0;     // bytes the pair pointer moves per stage (32 chunks)
     const int g_lane = p.g ? (gpow2 ? (lane >> gshift) : (lane * 32) / p.g) : 0;  // group of chunk `lane`
 
     const uint32_t wring = smem_u32(ring_base) + tid * 16;
     const uint32_t sring = smem_u32(ring_base + R_::kWBytes) + tid * 4;
-    const uint32_t tabs = ((smem_u32(ring_base + R_::kWBytes + R_::kSBytes) + 31u) & ~31u) + warp * (DEPTH * T * 32);
+    const uint32_t tabs = ((smem_u32(ring_base + R_::kWBytes + R_::kSBytes) + 255u) & ~255u) + warp * (DEPTH * 256);
     const uint32_t xs_u = smem_u32(xs) + lane * 16;
 
     const int first = rg_lo + warp;
@@ -287,11 +307,18 @@ __device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __hal
                     __syncwarp();  // nobody still reads the table buffer being replaced
                     if (lane < T * 2) {
                         const int row = min(irg * T + (lane >> 1), N - 1);
-                        cp_async16(tabs + itab * (T * 32) + lane * 16, p.codebook + (size_t)row * 16 + (lane & 1) * 8);
+                        cp_async16(tabs + itab * 256 + lane * 16, p.codebook + (size_t)row * 16 + (lane & 1) * 8);
                     }
                 }
             }
-            if (lane + 32 * ii < nchunks) {
+            if (FAST) {
+                const uint32_t live = (lane + 32 * ii < nchunks) ? 1u : 0u;
+#pragma unroll
+                for (int r = 0; r < T; ++r) {
+                    cp_async16_z(wring + (islot * T + r) * (kThreads * 16), wptr[r], live * 16u);
+                    cp_async4_z(sring + (islot * T + r) * (kThreads * 4), sptr[r], live * 4u);
+                }
+            } else if (lane + 32 * ii < nchunks) {
 #pragma unroll
                 for (int r = 0; r < T; ++r) {
                     cp_async16(wring + (islot * T + r) * (kThreads * 16), wptr[r]);
@@ -336,7 +363,7 @@ __device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __hal
             }
         }
         const int c = lane + 32 * ci;
-        if (c < nchunks) {
+        if (FAST || c < nchunks) {
             uint4 w[T];
             float sc[T];
             float part[T][B][2];
@@ -344,9 +371,9 @@ __device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __hal
             for (int r = 0; r < T; ++r) {
                 w[r] = lds128(wring + (cslot * T + r) * (kThreads * 16));
                 sc[r] = 1.f;
-                if (p.g) {
+                if (FAST || p.g) {
                     uint32_t hb;
-                    if (scale_async) {
+                    if (FAST || scale_async) {
                         hb = __byte_perm(lds32(sring + (cslot * T + r) * (kThreads * 4)), 0, sel[r]);
                     } else {
                         const int row = min(crg * T + r, N - 1);
@@ -367,7 +394,7 @@ __device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __hal
                 for (int r = 0; r < T; ++r) {
                     const uint32_t word = q == 0 ? w[r].x : (q == 1 ? w[r].y : (q == 2 ? w[r].z : w[r].w));
                     if (FMT == JQ_FMT_GF4) {
-                        dot8_gf4<B>(word, tabs + ctab * (T * 32) + r * 32, xv, part[r]);
+                        dot8_gf4<B>(word, tabs + ctab * 256, 0x20202020u * r, xv, part[r]);
                     } else if (B == 1) {
                         dot8_e2m1(word, xv[0], part[r][0][0], part[r][0][1]);
                     } else {
@@ -444,7 +471,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvProblem p, int x_
     constexpr int T = Tile<FMT, B>::R;
     const long long nrg = (p.N + T - 1) / T;
     const int lo = (int)(nrg * blockIdx.x / gridDim.x), hi = (int)(nrg * (blockIdx.x + 1) / gridDim.x);
-    cta_rows<FMT, B, DEPTH>(p, lo, hi, L.xs, L.sexp, L.ring, y_dtype);
+    if (fast_scales(p)) cta_rows<FMT, B, DEPTH, true>(p, lo, hi, L.xs, L.sexp, L.ring, y_dtype);
+    else cta_rows<FMT, B, DEPTH, false>(p, lo, hi, L.xs, L.sexp, L.ring, y_dtype);
 }
 
 struct PeerInfo {
@@ -491,7 +519,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_prob
         stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp);
         const int base = rg_start[pi];
         const int lim = min(rg_end, rg_start[pi + 1]);
-        cta_rows<FMT, B, DEPTH>(p, rg - base, lim - base, L.xs, L.sexp, L.ring, y_dtype);
+        if (fast_scales(p)) cta_rows<FMT, B, DEPTH, true>(p, rg - base, lim - base, L.xs, L.sexp, L.ring, y_dtype);
+        else cta_rows<FMT, B, DEPTH, false>(p, rg - base, lim - base, L.xs, L.sexp, L.ring, y_dtype);
         rg = lim;
         __syncthreads();  // all warps done with xs before the next problem restages it
     }
