@@ -54,11 +54,18 @@ constexpr int kWarps = kThreads / 32;
 #ifndef JQ_T_GF4
 #define JQ_T_GF4 4
 #endif
+#ifndef JQ_MMA_MINB
+#define JQ_MMA_MINB 2   // E2M1 batches from here up to 8 use the m16n8k16 row loop when the problem allows
+#endif
 template <int FMT, int B>
 struct Tile {
-    // rows a warp carries at once; bounded by registers and by the ring's shared memory
-    static constexpr int R = (B <= 2) ? (FMT == JQ_FMT_GF4 ? JQ_T_GF4 : JQ_T_E2M1) : (B <= 4 ? 2 : 1);
+    // rows a warp carries at once in the FMA row loops; bounded by registers and by the ring's shared memory
+    static constexpr int T = (B <= 2) ? (FMT == JQ_FMT_GF4 ? JQ_T_GF4 : JQ_T_E2M1) : (B <= 4 ? 2 : 1);
+    static constexpr bool kMma = FMT == JQ_FMT_E2M1 && B >= JQ_MMA_MINB;
+    // rows of a row group, the unit in which work is handed to warps (and planned on the host)
+    static constexpr int R = kMma ? 16 : T;
 };
+constexpr int kXPad = 32;  // halves between batch rows of the plain activation layout beyond xs_halves(K)
 
 // halves of shared memory one batch row of the activation occupies
 __host__ __device__ inline int xs_halves(int K) { return (jq_row_stride_codes(K) + 1023) / 1024 * 1024; }
@@ -84,10 +91,13 @@ __device__ __forceinline__ int act_exponent(float amax, bool had) {
 
 // CTA prologue: x[B,K] -> rotated, normalised fp16 in shared memory.
 // sred: kWarps floats of scratch; sexp: B ints (the exponents, kept for the epilogue).
+// plain: position of code k is k and batch rows are xs_halves(K) + kXPad halves
+// apart (the m16n8k16 row loop); otherwise the lane-interleaved layout above.
 template <int B>
-__device__ void stage_activation(const GemvProblem &p, int x_dtype, __half *xs, float *sred, int *sexp) {
+__device__ void stage_activation(const GemvProblem &p, int x_dtype, __half *xs, float *sred, int *sexp, bool plain = false) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = p.K, XS = xs_halves(K);
+    const int XSB = plain ? XS + kXPad : XS;
     for (int b = 0; b < B; ++b) {
         float m = 0.f;
         for (int k = tid; k < p.K_full; k += kThreads) m = fmaxf(m, fabsf(load_act(p.x_full, (size_t)b * p.ldx + k, x_dtype)));
@@ -104,7 +114,7 @@ __device__ void stage_activation(const GemvProblem &p, int x_dtype, __half *xs, 
     }
     for (int b = 0; b < B; ++b) {
         const float down = __uint_as_float((uint32_t)(127 - sexp[b]) << 23);  // 2^-e
-        __half *xb = xs + (size_t)b * XS;
+        __half *xb = xs + (size_t)b * XSB;
         if (p.had) {
             for (int blk = warp; blk * 128 < K; blk += kWarps) {
                 float v[4];
@@ -114,13 +124,13 @@ __device__ void stage_activation(const GemvProblem &p, int x_dtype, __half *xs, 
                 fwht128_warp(v, lane);
                 __half2 h01 = __floats2half2_rn(v[0], v[1]), h23 = __floats2half2_rn(v[2], v[3]);
                 uint2 pk = make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
-                *reinterpret_cast<uint2 *>(xb + xs_pos(k0)) = pk;
+                *reinterpret_cast<uint2 *>(xb + (plain ? k0 : xs_pos(k0))) = pk;
             }
         } else {
             for (int k = tid; k < K; k += kThreads)
-                xb[xs_pos(k)] = __float2half_rn(load_act(p.x, (size_t)b * p.ldx + k, x_dtype) * down);
+                xb[plain ? k : xs_pos(k)] = __float2half_rn(load_act(p.x, (size_t)b * p.ldx + k, x_dtype) * down);
         }
-        for (int k = K + tid; k < XS; k += kThreads) xb[xs_pos(k)] = __float2half_rn(0.f);
+        for (int k = K + tid; k < XS; k += kThreads) xb[plain ? k : xs_pos(k)] = __float2half_rn(0.f);
     }
     __syncthreads();
 }
@@ -233,7 +243,7 @@ __device__ __forceinline__ void dot8_gf4(uint32_t word, uint32_t tb, uint32_t rb
 
 template <int FMT, int B, int DEPTH>
 struct Ring {
-    static constexpr int T = Tile<FMT, B>::R;                       // rows per stage
+    static constexpr int T = Tile<FMT, B>::T;                       // rows per stage
     static constexpr int kSlots = DEPTH * T;                   // 16-byte slots per thread
     static constexpr int kWBytes = kSlots * kThreads * 16;     // weight ring
     static constexpr int kSBytes = kSlots * kThreads * 4;      // scale-pair ring
@@ -246,6 +256,40 @@ struct Ring {
 // Everything that is constant over a row group (row pointers, scale-pair
 // parity) is computed once per row group, so that a stage costs little beyond
 // its copies, its shared loads and the dot products themselves.
+// End of a row group: reduce the T x B partial sums over the warp, write the
+// outputs (and their copies into peer buffers), clear the accumulators.
+template <int T, int B>
+__device__ __forceinline__ void finish_rows(const GemvProblem &p, int crg, float (&acc)[T][B], int lane, const int *sexp,
+                                            int y_dtype) {
+    const int N = p.N;
+#pragma unroll
+    for (int r = 0; r < T; ++r)
+#pragma unroll
+        for (int b = 0; b < B; ++b) acc[r][b] = warp_sum(acc[r][b]);
+    // every lane holds every sum: lane (copy c, row r) = c * T + r writes row r into copy c of the
+    // output (copy 0 is the local buffer; further copies are peer GPUs' buffers, written over NVLink)
+    {
+        const int r_l = lane % T, c_l = lane / T;
+        const int row = crg * T + r_l;
+        if (c_l < p.npeer && row < N) {
+            const float bias = p.bias ? p.bias[row] : 0.f;
+            void *yc = reinterpret_cast<char *>(p.y) + p.peer_delta[c_l];
+#pragma unroll
+            for (int b = 0; b < B; ++b) {
+                float v = 0.f;
+#pragma unroll
+                for (int r = 0; r < T; ++r) v = (r == r_l) ? acc[r][b] : v;
+                const float up = __uint_as_float((uint32_t)(127 + sexp[b]) << 23);  // 2^e
+                store_out(yc, (size_t)b * p.ldy + row, fmaf(v, up, bias), y_dtype);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < T; ++r)
+#pragma unroll
+        for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
+}
+
 // FAST (the caller checked fast_scales(p)): group scales exist and are fetched
 // as aligned fp16 pairs by cp.async; the ragged end of a row is handled by
 // zero-filling copies instead of branches (zero codes and zero scales times
@@ -412,32 +456,7 @@ __device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __hal
         }
         cslot = (cslot + 1 == DEPTH) ? 0 : cslot + 1;
         if (++ci == nit) {
-#pragma unroll
-            for (int r = 0; r < T; ++r)
-#pragma unroll
-                for (int b = 0; b < B; ++b) acc[r][b] = warp_sum(acc[r][b]);
-            // every lane holds every sum: lane (copy c, row r) = c * T + r writes row r into copy c of the
-            // output (copy 0 is the local buffer; further copies are peer GPUs' buffers, written over NVLink)
-            {
-                const int r_l = lane % T, c_l = lane / T;
-                const int row = crg * T + r_l;
-                if (c_l < p.npeer && row < N) {
-                    const float bias = p.bias ? p.bias[row] : 0.f;
-                    void *yc = reinterpret_cast<char *>(p.y) + p.peer_delta[c_l];
-#pragma unroll
-                    for (int b = 0; b < B; ++b) {
-                        float v = 0.f;
-#pragma unroll
-                        for (int r = 0; r < T; ++r) v = (r == r_l) ? acc[r][b] : v;
-                        const float up = __uint_as_float((uint32_t)(127 + sexp[b]) << 23);  // 2^e
-                        store_out(yc, (size_t)b * p.ldy + row, fmaf(v, up, bias), y_dtype);
-                    }
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < T; ++r)
-#pragma unroll
-                for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
+            finish_rows<T, B>(p, crg, acc, lane, sexp, y_dtype);
             ci = 0;
             crg += kWarps;
             ctab = (ctab + 1 == DEPTH) ? 0 : ctab + 1;
@@ -445,6 +464,357 @@ __device__ void cta_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __hal
     }
     cp_async_wait<0>();
 }
+
+// GF4, groups present, batch 1..2: the shared-memory path is the bottleneck of
+// this format (one 16-bit table load per code), so the packed rows do not pass
+// through shared memory at all: every thread loads the 16 bytes (and the one
+// scale) it will consume one stage ahead into registers.  A stage of four rows
+// lasts longer than a DRAM round trip, so one stage in flight per thread (32 KB
+// per SM) is enough to cover the latency.  Only the per-row tables go through
+// shared memory (cp.async by the first 2T lanes, one 256-byte block per row
+// group, DEPTH blocks per warp).
+template <int B, int DEPTH>
+__device__ void cta_rows_gf4_direct(const GemvProblem &p, int rg_lo, int rg_hi, const __half *xs, const int *sexp,
+                                    unsigned char *ring_base, int y_dtype) {
+    using R_ = Ring<JQ_FMT_GF4, B, DEPTH>;
+    constexpr int T = R_::T;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = p.K, N = p.N, XS = xs_halves(K);
+    const int stride_b = p.ldw;
+    const int nchunks = jq_row_stride_codes(K) >> 5;
+    const int nit = (nchunks + 31) >> 5;
+    const int ngroups = p.lds;
+    const int gshift = 31 - __clz(p.g >> 5);
+    const int g_lane = lane >> gshift;                   // group of chunk `lane` within a stage
+    const int sadv = 1024 / p.g;                         // scales a stage advances by
+    const uint32_t tabs = ((smem_u32(ring_base + R_::kWBytes + R_::kSBytes) + 255u) & ~255u) + warp * (DEPTH * 256);
+    const uint32_t xs_u = smem_u32(xs) + lane * 16;
+
+    const int first = rg_lo + warp;
+    const int nrg = first < rg_hi ? (rg_hi - first + kWarps - 1) / kWarps : 0;
+    const int total = nrg * nit;
+
+    // ---- producer state: the stage whose loads are issued next ----
+    int is = 0, ii = 0, irg = first, itab = 0;
+    const uint8_t *wptr[T];
+    const __half *sptr[T];
+    auto fetch = [&](uint4 (&wn)[T], uint32_t (&sn)[T]) {
+        if (is < total) {
+            if (ii == 0) {
+#pragma unroll
+                for (int r = 0; r < T; ++r) {
+                    const int row = min(irg * T + r, N - 1);
+                    wptr[r] = p.qw + (size_t)row * stride_b + lane * 16;
+                    sptr[r] = p.scales + (size_t)row * ngroups + g_lane;
+                }
+                __syncwarp();  // nobody still reads the table block being replaced
+                if (lane < T * 2) {
+                    const int row = min(irg * T + (lane >> 1), N - 1);
+                    cp_async16(tabs + itab * 256 + lane * 16, p.codebook + (size_t)row * 16 + (lane & 1) * 8);
+                }
+                cp_async_commit();
+            }
+            const bool live = lane + 32 * ii < nchunks;
+#pragma unroll
+            for (int r = 0; r < T; ++r) {
+                wn[r] = make_uint4(0u, 0u, 0u, 0u);
+                sn[r] = 0u;
+                if (live) {
+                    wn[r] = ldg_stream_u4(wptr[r]);
+                    sn[r] = __ldg(reinterpret_cast<const unsigned short *>(sptr[r]));
+                }
+                wptr[r] += 512;
+                sptr[r] += sadv;
+            }
+            if (++ii == nit) { ii = 0; irg += kWarps; itab = (itab + 1 == DEPTH) ? 0 : itab + 1; }
+        }
+        ++is;
+    };
+
+    float acc[T][B];
+#pragma unroll
+    for (int r = 0; r < T; ++r)
+#pragma unroll
+        for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
+
+    // ---- consumer state ----
+    int ci = 0, crg = first, ctab = 0;
+    auto consume = [&](const uint4 (&w)[T], const uint32_t (&sn)[T]) {
+        if (ci == 0) {
+            cp_async_wait<0>();  // this row group's tables (copied by the first lanes one stage ago)
+            __syncwarp();
+        }
+        float part[T][B][2];
+#pragma unroll
+        for (int r = 0; r < T; ++r)
+#pragma unroll
+            for (int b = 0; b < B; ++b) part[r][b][0] = part[r][b][1] = 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint4 xv[B];
+#pragma unroll
+            for (int b = 0; b < B; ++b) xv[b] = lds128(xs_u + (uint32_t)(b * XS + (((ci * 4 + q) * 32) << 3)) * 2);
+#pragma unroll
+            for (int r = 0; r < T; ++r) {
+                const uint32_t word = q == 0 ? w[r].x : (q == 1 ? w[r].y : (q == 2 ? w[r].z : w[r].w));
+                dot8_gf4<B>(word, tabs + ctab * 256, 0x20202020u * r, xv, part[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < T; ++r) {
+            const float sc = __half2float(__ushort_as_half((unsigned short)sn[r]));
+#pragma unroll
+            for (int b = 0; b < B; ++b) acc[r][b] = fmaf(part[r][b][0] + part[r][b][1], sc, acc[r][b]);
+        }
+        if (++ci == nit) {
+            finish_rows<T, B>(p, crg, acc, lane, sexp, y_dtype);
+            ci = 0;
+            crg += kWarps;
+            ctab = (ctab + 1 == DEPTH) ? 0 : ctab + 1;
+        }
+    };
+
+    uint4 wa[T], wb[T];
+    uint32_t sa[T], sb[T];
+    fetch(wa, sa);
+    for (int s = 0; s < total; s += 2) {
+        fetch(wb, sb);
+        consume(wa, sa);
+        fetch(wa, sa);
+        if (s + 1 < total) consume(wb, sb);
+    }
+    cp_async_wait<0>();
+}
+
+// ---- E2M1, batch 2..8: the dot products on mma.sync.m16n8k16 ---------------------
+// With more than one batch row the FMA loops above pay one FMA per code and
+// batch row and become issue bound.  Here a warp owns 16 rows; the decoded fp16
+// weights are the A operand (16 rows x 16 codes) and the staged fp16 activation
+// the B operand (16 codes x 8 batch columns) of the legacy warp-level MMA, which
+// costs one instruction per 256 codes whatever the batch (up to 8).  Products
+// fp16 x fp16 and the fp32 accumulation stay as in the FMA loops.  The group
+// scale (one per row and 32 codes) cannot enter the MMA, so every 32-code chunk
+// (two MMAs) starts from a zero accumulator and is folded into the running sum
+// with one fp32 FMA per output.  Thread (g = lane / 4, t = lane % 4) feeds rows
+// g and g + 8 with the 8 codes of 32-bit word t of the chunk and batch column g
+// with the matching 8 activations; it ends up with the finished sums of rows
+// g, g + 8 x batch columns 2t, 2t + 1: no reduction across lanes at all.
+//
+// Staging: a stage is 16 rows x 8 chunks (128 bytes per row), copied with four
+// 16-byte cp.async per lane into a per-warp slot whose 16-byte columns are
+// XOR-swizzled by the row so that the fragment reads (one 32-bit word per lane)
+// hit 32 different banks; the stage's 16 x 8 scales follow with one more copy
+// by the first 16 lanes.  Lanes consume what other lanes copied, so one
+// __syncwarp per stage orders the ring; nothing spins.
+constexpr int kMmaStageBytes = 16 * 128 + 16 * 16;  // weights + scales
+
+template <int DEPTH>
+struct MmaRing {
+    static constexpr int kCombBytes = 2 * kWarps * 32 * 16;   // partial sums of K parts: two rounds x warps x lanes x 4 floats
+    static constexpr int kBytes = kWarps * DEPTH * kMmaStageBytes + kCombBytes + 128;  // + slack to start at a 128-byte boundary
+};
+
+// The problem suits the MMA row loop: one scale per 32-code chunk, whole
+// 8-chunk stages, 16-byte aligned scale rows.
+__device__ __forceinline__ bool mma_ok(const GemvProblem &p) {
+    return p.g == 32 && (p.K & 255) == 0 && (p.lds & 7) == 0 && (reinterpret_cast<uintptr_t>(p.scales) & 15u) == 0;
+}
+
+// K parts a row group is cut into (a function of K alone, so that every launch
+// and every row shard of a matrix sums in the same order): 16 rows x all of K
+// is a coarse unit of work for 16 warps per SM, and a row group's parts run on
+// adjacent warps in the same round.
+__host__ __device__ inline int mma_ksplit_log2(int K) {
+    const int nit = K >> 8;
+    return (nit >= 8 && (nit & 3) == 0) ? 2 : ((nit >= 4 && (nit & 1) == 0) ? 1 : 0);
+}
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1, const float (&c)[4]) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+template <int B, int DEPTH>
+__device__ void cta_rows_mma(const GemvProblem &p, int rg_lo, int rg_hi, const __half *xs, const int *sexp,
+                             unsigned char *ring_base, int y_dtype) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int N = p.N, XSB = xs_halves(p.K) + kXPad;
+    const int nit = p.K >> 8;                            // stages (8 chunks of 32 codes) per row
+    // 128-byte aligned slots (a stage is a multiple of 128 bytes), so that bits 4..6 of a row's address are free
+    const uint32_t ring = ((smem_u32(ring_base) + 127u) & ~127u) + warp * (DEPTH * kMmaStageBytes);
+    // producer addressing: copy i of a stage moves chunk (lane & 7) of row (lane >> 3) + 4 i
+    const int prow = lane >> 3, pch = lane & 7;
+    // consumer addressing: chunk c of row g sits in 16-byte column c ^ g, i.e. at (base | g << 4) ^ (c << 4)
+    const uint32_t cw = ring + g * 128 + (g << 4) + t * 4;           // ^ (c << 4); + 1024 for row g + 8
+    const uint32_t cs = ring + 2048 + g * 16;                        // scales of row g; + 128 for row g + 8
+    // batch columns beyond B read batch row B - 1: their outputs are never stored
+    const uint32_t xs_u = smem_u32(xs) + (uint32_t)(min(g, B - 1) * XSB + t * 8) * 2;
+
+    // a task = (row group, K part); part q of a row group covers stages [q nitp, (q + 1) nitp)
+    const int ksh = mma_ksplit_log2(p.K), ks = 1 << ksh, nitp = nit >> ksh;
+    const int first = (rg_lo << ksh) + warp, task_end = rg_hi << ksh;
+    const int ntask = first < task_end ? (task_end - first + kWarps - 1) / kWarps : 0;
+    const int total = ntask * nitp;
+    float4 *comb = reinterpret_cast<float4 *>(ring_base + (MmaRing<DEPTH>::kBytes - MmaRing<DEPTH>::kCombBytes));
+
+    // ---- producer state ----
+    int is = 0, ii = 0, itask = first, islot = 0;
+    const uint8_t *wptr[4];
+    const __half *sptr = nullptr;
+    auto issue = [&]() {
+        if (is < total) {
+            if (ii == 0) {
+                const int rg = itask >> ksh, part = itask & (ks - 1);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = min(rg * 16 + 4 * i + prow, N - 1);
+                    wptr[i] = p.qw + (size_t)row * p.ldw + (part * nitp * 8 + pch) * 16;
+                }
+                sptr = p.scales + (size_t)min(rg * 16 + (lane & 15), N - 1) * p.lds + part * nitp * 8;
+            }
+            const uint32_t slot = islot * kMmaStageBytes;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                // row 4 i + prow: its swizzle key is (row & 7) = (4 i + prow) & 7
+                const uint32_t key = (uint32_t)((4 * i + prow) & 7);
+                cp_async16(ring + slot + (4 * i + prow) * 128 + ((pch ^ key) << 4), wptr[i]);
+                wptr[i] += 128;
+            }
+            if (lane < 16) cp_async16(ring + slot + 2048 + lane * 16, sptr);
+            sptr += 8;
+            if (++ii == nitp) { ii = 0; itask += kWarps; }
+        }
+        ++is;
+        islot = (islot + 1 == DEPTH) ? 0 : islot + 1;
+        cp_async_commit();
+    };
+
+#pragma unroll
+    for (int d = 0; d < DEPTH - 1; ++d) issue();
+
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+    int ci = 0, ctask = first, cslot = 0, cpar = 0;
+    for (int s = 0; s < total; ++s) {
+        cp_async_wait<DEPTH - 2>();   // this thread's copies of stage s have landed
+        __syncwarp();                 // ... and everyone's; everyone has also finished reading stage s - 1
+        issue();                      // refills the slot of stage s - 1
+        const uint32_t slot = cslot * kMmaStageBytes;
+        const uint4 sa = lds128(cs + slot), sb = lds128(cs + slot + 128);   // 8 scales of rows g and g + 8
+        const uint32_t xbase = xs_u + (uint32_t)(((ctask & (ks - 1)) * nitp + ci) * 256) * 2;
+        const uint32_t cwslot = cw + slot;
+#pragma unroll
+        for (int c2 = 0; c2 < 4; ++c2) {
+            const uint32_t pa = c2 == 0 ? sa.x : (c2 == 1 ? sa.y : (c2 == 2 ? sa.z : sa.w));
+            const uint32_t pb = c2 == 0 ? sb.x : (c2 == 1 ? sb.y : (c2 == 2 ? sb.z : sb.w));
+            const float2 fa = __half22float2(*reinterpret_cast<const __half2 *>(&pa));
+            const float2 fb = __half22float2(*reinterpret_cast<const __half2 *>(&pb));
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int c = 2 * c2 + j;
+                const uint32_t a = cwslot ^ (uint32_t)(c << 4);
+                const uint32_t wa = lds32(a), wb = lds32(a + 1024);
+                const uint4 xv = lds128(xbase + c * 64);
+                uint32_t ha[4], hb[4];
+                cvt8_e2m1(wa, ha);
+                cvt8_e2m1(wb, hb);
+                float d[4];
+                mma16816(d, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y, zero);
+                mma16816(d, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w, d);
+                const float sca = j ? fa.y : fa.x, scb = j ? fb.y : fb.x;
+                acc[0] = fmaf(d[0], sca, acc[0]);
+                acc[1] = fmaf(d[1], sca, acc[1]);
+                acc[2] = fmaf(d[2], scb, acc[2]);
+                acc[3] = fmaf(d[3], scb, acc[3]);
+            }
+        }
+        cslot = (cslot + 1 == DEPTH) ? 0 : cslot + 1;
+        if (++ci == nitp) {
+            // acc = this K part's sums of rows g, g + 8 x batch columns 2t, 2t + 1
+            bool writer = true;
+            if (ks > 1) {
+                // the parts of a row group sit on ks adjacent warps in the same round: all but the first
+                // park their sums in shared memory (two alternating sets, so that a set is never rewritten
+                // before its reader has passed the next round's barrier), the first adds them in part order
+                writer = (warp & (ks - 1)) == 0;
+                float4 *mine = comb + (cpar * kWarps + warp) * 32 + lane;
+                if (!writer) *mine = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + (warp >> ksh)), "r"(ks * 32) : "memory");
+                if (writer) {
+                    for (int q = 1; q < ks; ++q) {
+                        const float4 o = mine[q * 32];
+                        acc[0] += o.x; acc[1] += o.y; acc[2] += o.z; acc[3] += o.w;
+                    }
+                }
+                cpar ^= 1;
+            }
+            if (writer) {
+                const int rg = ctask >> ksh;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int row = rg * 16 + g + 8 * h;
+                    if (row < N) {
+                        const float bias = p.bias ? p.bias[row] : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const int b = 2 * t + j;
+                            if (b < B) {
+                                const float up = __uint_as_float((uint32_t)(127 + sexp[b]) << 23);  // 2^e
+                                const float v = fmaf(acc[2 * h + j], up, bias);
+                                for (int cpy = 0; cpy < p.npeer; ++cpy)
+                                    store_out(reinterpret_cast<char *>(p.y) + p.peer_delta[cpy], (size_t)b * p.ldy + row, v, y_dtype);
+                            }
+                        }
+                    }
+                }
+            }
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+            ci = 0;
+            ctask += kWarps;
+        }
+    }
+    cp_async_wait<0>();
+}
+
+#ifndef JQ_GF4_DIRECT_MAXB
+#define JQ_GF4_DIRECT_MAXB 1
+#endif
+// the row loop that suits the problem (uniform over the CTA)
+template <int FMT, int B, int DEPTH>
+__device__ __forceinline__ void run_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __half *xs, const int *sexp,
+                                         unsigned char *ring_base, int y_dtype) {
+    if constexpr (Tile<FMT, B>::kMma) {
+        if (mma_ok(p)) {
+            cta_rows_mma<B, DEPTH>(p, rg_lo, rg_hi, xs, sexp, ring_base, y_dtype);
+            return;
+        }
+    }
+    // the FMA loops count row groups of Tile::T rows
+    constexpr int kSub = Tile<FMT, B>::R / Tile<FMT, B>::T;
+    rg_lo *= kSub;
+    rg_hi *= kSub;
+    if (fast_scales(p)) {
+        if constexpr (FMT == JQ_FMT_GF4 && B <= JQ_GF4_DIRECT_MAXB)
+            cta_rows_gf4_direct<B, DEPTH>(p, rg_lo, rg_hi, xs, sexp, ring_base, y_dtype);
+        else
+            cta_rows<FMT, B, DEPTH, true>(p, rg_lo, rg_hi, xs, sexp, ring_base, y_dtype);
+    } else {
+        cta_rows<FMT, B, DEPTH, false>(p, rg_lo, rg_hi, xs, sexp, ring_base, y_dtype);
+    }
+}
+
+// shared memory of the row loops a kernel instance may run: the larger ring,
+// the wider activation rows
+template <int FMT, int B, int DEPTH>
+__host__ __device__ constexpr int ring_bytes() {
+    return (Tile<FMT, B>::kMma && MmaRing<DEPTH>::kBytes > Ring<FMT, B, DEPTH>::kBytes) ? MmaRing<DEPTH>::kBytes
+                                                                                     : Ring<FMT, B, DEPTH>::kBytes;
+}
+template <int FMT, int B>
+__host__ __device__ inline int xs_stride(int K) { return xs_halves(K) + (Tile<FMT, B>::kMma ? kXPad : 0); }
 
 struct SmemLayout {
     __half *xs;
@@ -457,8 +827,8 @@ template <int FMT, int B, int DEPTH>
 __device__ __forceinline__ SmemLayout carve(unsigned char *smem, int maxK) {
     SmemLayout L;
     L.ring = smem;  // 16-byte aligned slots first
-    L.xs = reinterpret_cast<__half *>(smem + Ring<FMT, B, DEPTH>::kBytes);
-    L.sred = reinterpret_cast<float *>(L.xs + (size_t)B * xs_halves(maxK));
+    L.xs = reinterpret_cast<__half *>(smem + ring_bytes<FMT, B, DEPTH>());
+    L.sred = reinterpret_cast<float *>(L.xs + (size_t)B * xs_stride<FMT, B>(maxK));
     L.sexp = reinterpret_cast<int *>(L.sred + kWarps);
     return L;
 }
@@ -467,12 +837,11 @@ template <int FMT, int B, int DEPTH>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvProblem p, int x_dtype, int y_dtype) {
     extern __shared__ __align__(16) unsigned char smem[];
     const SmemLayout L = carve<FMT, B, DEPTH>(smem, p.K);
-    stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp);
+    stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp, Tile<FMT, B>::kMma && mma_ok(p));
     constexpr int T = Tile<FMT, B>::R;
     const long long nrg = (p.N + T - 1) / T;
     const int lo = (int)(nrg * blockIdx.x / gridDim.x), hi = (int)(nrg * (blockIdx.x + 1) / gridDim.x);
-    if (fast_scales(p)) cta_rows<FMT, B, DEPTH, true>(p, lo, hi, L.xs, L.sexp, L.ring, y_dtype);
-    else cta_rows<FMT, B, DEPTH, false>(p, lo, hi, L.xs, L.sexp, L.ring, y_dtype);
+    run_rows<FMT, B, DEPTH>(p, lo, hi, L.xs, L.sexp, L.ring, y_dtype);
 }
 
 struct PeerInfo {
@@ -516,11 +885,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_prob
         p.npeer = peers.n;
 #pragma unroll
         for (int i = 0; i < 8; ++i) p.peer_delta[i] = peers.delta[i];
-        stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp);
+        stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp, Tile<FMT, B>::kMma && mma_ok(p));
         const int base = rg_start[pi];
         const int lim = min(rg_end, rg_start[pi + 1]);
-        if (fast_scales(p)) cta_rows<FMT, B, DEPTH, true>(p, rg - base, lim - base, L.xs, L.sexp, L.ring, y_dtype);
-        else cta_rows<FMT, B, DEPTH, false>(p, rg - base, lim - base, L.xs, L.sexp, L.ring, y_dtype);
+        run_rows<FMT, B, DEPTH>(p, rg - base, lim - base, L.xs, L.sexp, L.ring, y_dtype);
         rg = lim;
         __syncthreads();  // all warps done with xs before the next problem restages it
     }
@@ -528,7 +896,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_prob
 
 template <int FMT, int B, int DEPTH>
 static size_t gemv_smem_bytes(int K) {
-    return (size_t)Ring<FMT, B, DEPTH>::kBytes + (size_t)B * xs_halves(K) * 2 + kWarps * 4 + 8 * 4;
+    return (size_t)ring_bytes<FMT, B, DEPTH>() + (size_t)B * xs_stride<FMT, B>(K) * 2 + kWarps * 4 + 8 * 4;
 }
 
 }  // namespace jq
@@ -573,6 +941,8 @@ static int launch_gemv_d(const GemvProblem &p, int x_dtype, int y_dtype, cudaStr
 template <int FMT, int B>
 static int launch_gemv(const GemvProblem &p, int x_dtype, int y_dtype, cudaStream_t st) {
     if (gemv_smem_bytes<FMT, B, 4>(p.K) <= kMaxSmem) return launch_gemv_d<FMT, B, 4>(p, x_dtype, y_dtype, st);
+    if constexpr (Tile<FMT, B>::kMma)
+        if (gemv_smem_bytes<FMT, B, 3>(p.K) <= kMaxSmem) return launch_gemv_d<FMT, B, 3>(p, x_dtype, y_dtype, st);
     return launch_gemv_d<FMT, B, 2>(p, x_dtype, y_dtype, st);
 }
 
@@ -822,6 +1192,9 @@ static int launch_grouped(const jq_problem *pd, const int *plan_host, const int 
                           const PeerInfo &peers, cudaStream_t st) {
     if (gemv_smem_bytes<FMT, B, 4>(plan_host[3]) <= kMaxSmem)
         return launch_grouped_d<FMT, B, 4>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
+    if constexpr (Tile<FMT, B>::kMma)
+        if (gemv_smem_bytes<FMT, B, 3>(plan_host[3]) <= kMaxSmem)
+            return launch_grouped_d<FMT, B, 3>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
     return launch_grouped_d<FMT, B, 2>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
 }
 

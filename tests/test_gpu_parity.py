@@ -115,6 +115,39 @@ def test_gemv_parity_shapes(N, K, fmt, g, had):
     _check_gemv(pw, torch.randn(2, K, generator=gen).half())
 
 
+@pytest.mark.parametrize("N,K,had", [(16, 256, 0), (5, 256, 128), (203, 1024, 0), (48, 2048, 128), (33, 11008, 0),
+                                     (1000, 4096, 128), (17, 8192, 0)])
+@pytest.mark.parametrize("B", [2, 3, 7, 8])
+def test_e2m1_batched_rows_on_the_mma_loop(N, K, had, B):
+    """E2M1 g32, K a multiple of 256, batch 2..8: the m16n8k16 row loop, with one, two or four K parts per
+    row group (K = 256 / 1024 / 2048+), ragged N, rotation on and off."""
+    pw = jq.pack_weight(_weights(N, K, N + 3 * K), jq.QuantSpec("e2m1", 32, had))
+    gen = torch.Generator("cpu").manual_seed(N + B)
+    _check_gemv(pw, torch.randn(B, K, generator=gen).bfloat16(), torch.randn(N, generator=gen))
+
+
+def test_e2m1_batched_fallbacks_and_row_shards_agree_bit_for_bit():
+    gen = torch.Generator("cpu").manual_seed(9)
+    # not eligible for the MMA loop (K % 256 != 0, or 64-code groups): the FMA loops take them
+    for K, g in ((1152, 32), (1024, 64)):
+        pw = jq.pack_weight(_weights(70, K, K), jq.QuantSpec("e2m1", g, 0))
+        _check_gemv(pw, torch.randn(5, K, generator=gen).half())
+    # a row shard computes exactly what the whole matrix computes for those rows (same summation order)
+    pw = jq.pack_weight(_weights(320, 4096, 5), jq.QuantSpec("e2m1", 32, 128)).to(DEV)
+    x = torch.randn(6, 4096, generator=gen).bfloat16().to(DEV)
+    y = ops.linear(x, pw, out_dtype=torch.float32)
+    for lo, hi in ((0, 160), (160, 320), (37, 90)):
+        assert torch.equal(ops.linear(x, pw.rows(lo, hi), out_dtype=torch.float32), y[:, lo:hi])
+    # unit vectors: exact columns of the dequantised matrix, every batch row its own column
+    w_hat = ops.dequantize(pw)
+    ks = [0, 1, 31, 32, 255, 256, 4095]
+    xe = torch.zeros(len(ks), 4096, device=DEV)
+    for i, k in enumerate(ks):
+        xe[i, k] = 1.0
+    pw0 = jq.pack_weight(_weights(320, 4096, 5), jq.QuantSpec("e2m1", 32, 0)).to(DEV)
+    assert torch.equal(ops.linear(xe, pw0), ops.dequantize(pw0)[:, ks].t().contiguous())
+
+
 def test_gemv_heavy_tailed_activations_and_extreme_magnitudes():
     K = 4096
     pw = jq.pack_weight(_weights(256, K, 2), jq.QuantSpec("gf4", 128, 128))
