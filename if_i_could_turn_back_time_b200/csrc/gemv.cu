@@ -94,11 +94,12 @@ __device__ __forceinline__ int act_exponent(float amax, bool had) {
 // plain: position of code k is k and batch rows are xs_halves(K) + kXPad halves
 // apart (the m16n8k16 row loop); otherwise the lane-interleaved layout above.
 template <int B>
-__device__ void stage_activation(const GemvProblem &p, int x_dtype, __half *xs, float *sred, int *sexp, bool plain = false) {
+__device__ void stage_activation(const GemvProblem &p, int x_dtype, __half *xs, float *sred, int *sexp, bool plain = false,
+                                 bool keep_exponents = false) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = p.K, XS = xs_halves(K);
     const int XSB = plain ? XS + kXPad : XS;
-    for (int b = 0; b < B; ++b) {
+    for (int b = 0; b < B && !keep_exponents; ++b) {   // (a later K tile of the same rows: sexp[] is already right)
         float m = 0.f;
         for (int k = tid; k < p.K_full; k += kThreads) m = fmaxf(m, fabsf(load_act(p.x_full, (size_t)b * p.ldx + k, x_dtype)));
 #pragma unroll
@@ -638,7 +639,8 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
 
 template <int B, int DEPTH>
 __device__ void cta_rows_mma(const GemvProblem &p, int rg_lo, int rg_hi, const __half *xs, const int *sexp,
-                             unsigned char *ring_base, int y_dtype) {
+                             unsigned char *ring_base, int y_dtype, float *partial = nullptr, int partial_rg0 = 0,
+                             bool partial_first = true) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int N = p.N, XSB = xs_halves(p.K) + kXPad;
@@ -751,7 +753,20 @@ __device__ void cta_rows_mma(const GemvProblem &p, int rg_lo, int rg_hi, const _
                 }
                 cpar ^= 1;
             }
-            if (writer) {
+            if (writer && partial) {
+                // one K tile of several: the sums go to the chunk's [row][batch] table in shared memory
+                const int rg = ctask >> ksh;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int b = 2 * t + j;
+                        if (b < B) {
+                            float *dst = partial + ((rg - partial_rg0) * 16 + g + 8 * h) * B + b;
+                            *dst = partial_first ? acc[2 * h + j] : *dst + acc[2 * h + j];
+                        }
+                    }
+            } else if (writer) {
                 const int rg = ctask >> ksh;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
@@ -823,20 +838,61 @@ struct SmemLayout {
     unsigned char *ring;
 };
 
+constexpr int kSmallBytes = kWarps * 4 + 8 * 4;  // reduction scratch + exponents
 template <int FMT, int B, int DEPTH>
-__device__ __forceinline__ SmemLayout carve(unsigned char *smem, int maxK) {
+__device__ __forceinline__ SmemLayout carve(unsigned char *smem) {
     SmemLayout L;
     L.ring = smem;  // 16-byte aligned slots first
-    L.xs = reinterpret_cast<__half *>(smem + ring_bytes<FMT, B, DEPTH>());
-    L.sred = reinterpret_cast<float *>(L.xs + (size_t)B * xs_stride<FMT, B>(maxK));
+    L.sred = reinterpret_cast<float *>(smem + ring_bytes<FMT, B, DEPTH>());
     L.sexp = reinterpret_cast<int *>(L.sred + kWarps);
+    L.xs = reinterpret_cast<__half *>(L.sexp + 8);  // the staged activation takes the rest
     return L;
+}
+
+// B x K halves do not fit in the activation region (xcap halves): the CTA walks
+// its row groups in chunks and, per chunk, the K range in tiles.  Each tile's
+// activation is staged in the first half of the region, the chunk's partial
+// sums (fp32, [row][batch]) live in the rest and are turned into outputs after
+// the last tile.  The normalisation exponent is that of the whole row, so the
+// tiles add up in one scale.
+template <int B, int DEPTH>
+__device__ void rows_k_tiled(const GemvProblem &p, int rg_lo, int rg_hi, const SmemLayout &L, int xcap, int x_dtype,
+                             int y_dtype) {
+    const int tileK = ((xcap / 2) / B - kXPad) / 1024 * 1024;
+    const int xuse = (B * (tileK + kXPad) + 7) & ~7;              // halves, keeps the partial sums 16-byte aligned
+    float *partial = reinterpret_cast<float *>(L.xs + xuse);
+    const int chunk = ((xcap - xuse) / 2) / (16 * B);             // row groups whose partial sums fit
+    if (tileK < 1024 || chunk < 1) return;                        // (the host never launches such a case)
+    const size_t xe = x_dtype == JQ_F32 ? 4 : 2;
+    for (int c0 = rg_lo; c0 < rg_hi; c0 += chunk) {
+        const int c1 = min(rg_hi, c0 + chunk);
+        for (int k0 = 0; k0 < p.K; k0 += tileK) {
+            GemvProblem q = p;
+            q.K = min(tileK, p.K - k0);
+            q.qw = p.qw + (k0 >> 1);
+            q.scales = p.scales + (k0 >> 5);
+            q.x = reinterpret_cast<const char *>(p.x) + (size_t)k0 * xe;
+            __syncthreads();  // the previous tile's activation is no longer read
+            stage_activation<B>(q, x_dtype, L.xs, L.sred, L.sexp, true, !(c0 == rg_lo && k0 == 0));
+            cta_rows_mma<B, DEPTH>(q, c0, c1, L.xs, L.sexp, L.ring, y_dtype, partial, c0, k0 == 0);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < (c1 - c0) * 16 * B; i += kThreads) {
+            const int row = c0 * 16 + i / B, b = i % B;
+            if (row < p.N) {
+                const float up = __uint_as_float((uint32_t)(127 + L.sexp[b]) << 23);  // 2^e
+                const float v = fmaf(partial[i], up, p.bias ? p.bias[row] : 0.f);
+                for (int cpy = 0; cpy < p.npeer; ++cpy)
+                    store_out(reinterpret_cast<char *>(p.y) + p.peer_delta[cpy], (size_t)b * p.ldy + row, v, y_dtype);
+            }
+        }
+    }
 }
 
 template <int FMT, int B, int DEPTH>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvProblem p, int x_dtype, int y_dtype) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const SmemLayout L = carve<FMT, B, DEPTH>(smem, p.K);
+    const SmemLayout L = carve<FMT, B, DEPTH>(smem);
     stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp, Tile<FMT, B>::kMma && mma_ok(p));
     constexpr int T = Tile<FMT, B>::R;
     const long long nrg = (p.N + T - 1) / T;
@@ -858,10 +914,10 @@ struct PeerInfo {
 template <int FMT, int B, int DEPTH>
 __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_problem *probs, int nprob,
                                                                      const int *rg_start, const int *cta_first,
-                                                                     int maxK, int x_dtype, int y_dtype, PeerInfo peers) {
+                                                                     int xcap, int x_dtype, int y_dtype, PeerInfo peers) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int s_prob;
-    const SmemLayout L = carve<FMT, B, DEPTH>(smem, maxK);
+    const SmemLayout L = carve<FMT, B, DEPTH>(smem);
     int rg = cta_first[blockIdx.x];
     const int rg_end = cta_first[blockIdx.x + 1];
     int pi = 0;
@@ -885,10 +941,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_prob
         p.npeer = peers.n;
 #pragma unroll
         for (int i = 0; i < 8; ++i) p.peer_delta[i] = peers.delta[i];
-        stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp, Tile<FMT, B>::kMma && mma_ok(p));
         const int base = rg_start[pi];
         const int lim = min(rg_end, rg_start[pi + 1]);
-        run_rows<FMT, B, DEPTH>(p, rg - base, lim - base, L.xs, L.sexp, L.ring, y_dtype);
+        bool tiled = false;
+        if constexpr (Tile<FMT, B>::kMma) tiled = B * xs_stride<FMT, B>(p.K) > xcap && mma_ok(p);
+        if (!tiled) {
+            stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp, Tile<FMT, B>::kMma && mma_ok(p));
+            run_rows<FMT, B, DEPTH>(p, rg - base, lim - base, L.xs, L.sexp, L.ring, y_dtype);
+        } else if constexpr (Tile<FMT, B>::kMma) {
+            rows_k_tiled<B, DEPTH>(p, rg - base, lim - base, L, xcap, x_dtype, y_dtype);
+        }
         rg = lim;
         __syncthreads();  // all warps done with xs before the next problem restages it
     }
@@ -896,7 +958,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_prob
 
 template <int FMT, int B, int DEPTH>
 static size_t gemv_smem_bytes(int K) {
-    return (size_t)ring_bytes<FMT, B, DEPTH>() + (size_t)B * xs_stride<FMT, B>(K) * 2 + kWarps * 4 + 8 * 4;
+    return (size_t)ring_bytes<FMT, B, DEPTH>() + (size_t)B * xs_stride<FMT, B>(K) * 2 + kSmallBytes;
 }
 
 }  // namespace jq
@@ -921,7 +983,7 @@ static int validate_problem(int fmt, const void *qw, const void *scales, const v
 
 static bool dtype_ok(int d) { return d == JQ_F32 || d == JQ_F16 || d == JQ_BF16; }
 
-static const size_t kMaxSmem = 227 * 1024;
+static const size_t kMaxSmem = 227 * 1024 - 64;  // dynamic part: the grouped kernel also has a few static bytes
 
 template <int FMT, int B, int DEPTH>
 static int launch_gemv_d(const GemvProblem &p, int x_dtype, int y_dtype, cudaStream_t st) {
@@ -1099,7 +1161,9 @@ extern "C" int jq_gemv_gf4(const void *qweight, const void *scales, const void *
 }
 
 // ---- grouped launch ---------------------------------------------------------
-// plan layout (ints): [magic, n, grid, maxK, R, B, fmt, 0] rg_start[n+1] cta_first[grid+1]
+// plan layout (ints): [magic, n, grid, maxK, R, B, fmt, maxK_whole] rg_start[n+1] cta_first[grid+1]
+// (maxK_whole: the largest K among problems whose activation must be staged whole, i.e. that the K-tiled
+// MMA row loop cannot take)
 static const int kPlanMagic = 0x4a51504c;
 static const int kPlanHeader = 8;
 
@@ -1131,9 +1195,10 @@ extern "C" int jq_grouped_plan(int fmt, const jq_problem *ph, int n, int B, void
     const int grid = jq_sm_count();  // one persistent CTA per SM
     int *h = reinterpret_cast<int *>(plan_host);
     int *rg_start = h + kPlanHeader, *cta_first = rg_start + n + 1;
-    int maxK = 0;
+    int maxK = 0, maxK_whole = 0;
     double total = 0;
     rg_start[0] = 0;
+    const bool mma_fmt = fmt == JQ_FMT_E2M1 && B >= JQ_MMA_MINB;
     for (int i = 0; i < n; ++i) {
         int st = validate_problem(fmt, ph[i].qweight, ph[i].scales, ph[i].codebook, ph[i].x, ph[i].y, ph[i].N,
                                   ph[i].K, ph[i].g, ph[i].had_block);
@@ -1143,6 +1208,9 @@ extern "C" int jq_grouped_plan(int fmt, const jq_problem *ph, int n, int B, void
         rg_start[i + 1] = rg_start[i] + (int)groups;
         total += (double)groups * ph[i].K;
         maxK = ph[i].K > maxK ? ph[i].K : maxK;
+        const bool tileable = mma_fmt && ph[i].g == 32 && (ph[i].K & 255) == 0 &&
+                              (reinterpret_cast<uintptr_t>(ph[i].scales) & 15u) == 0;  // = mma_ok() on the device
+        if (!tileable && ph[i].K > maxK_whole) maxK_whole = ph[i].K;
     }
     // contiguous CTA ranges of (nearly) equal packed bytes: cut every total/grid
     // units of row-groups * K while walking the problems in order
@@ -1171,7 +1239,7 @@ extern "C" int jq_grouped_plan(int fmt, const jq_problem *ph, int n, int B, void
         }
     }
     for (int c = cta + 1; c <= grid; ++c) cta_first[c] = rg_start[n];
-    h[0] = kPlanMagic; h[1] = n; h[2] = grid; h[3] = maxK; h[4] = R; h[5] = B; h[6] = fmt; h[7] = 0;
+    h[0] = kPlanMagic; h[1] = n; h[2] = grid; h[3] = maxK; h[4] = R; h[5] = B; h[6] = fmt; h[7] = maxK_whole;
     return JQ_OK;
 }
 
@@ -1179,11 +1247,16 @@ template <int FMT, int B, int DEPTH>
 static int launch_grouped_d(const jq_problem *pd, const int *plan_host, const int *plan_dev, int x_dtype, int y_dtype,
                             const PeerInfo &peers, cudaStream_t st) {
     const int n = plan_host[1], grid = plan_host[2], maxK = plan_host[3];
-    const size_t smem = gemv_smem_bytes<FMT, B, DEPTH>(maxK);
-    if (smem > kMaxSmem) return JQ_ERR_UNSUPPORTED;
+    size_t smem = gemv_smem_bytes<FMT, B, DEPTH>(maxK);
+    if (smem > kMaxSmem) {
+        // K-tiled problems: all the shared memory there is; the kernel splits the activation region
+        if (!Tile<FMT, B>::kMma || gemv_smem_bytes<FMT, B, DEPTH>(plan_host[7]) > kMaxSmem) return JQ_ERR_UNSUPPORTED;
+        smem = kMaxSmem;
+    }
+    const int xcap = (int)((smem - ring_bytes<FMT, B, DEPTH>() - kSmallBytes) / 2);  // halves for the activation
     auto kern = gemv_grouped_kernel<FMT, B, DEPTH>;
     JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kThreads, smem, st>>>(pd, n, plan_dev + kPlanHeader, plan_dev + kPlanHeader + n + 1, maxK, x_dtype, y_dtype, peers);
+    kern<<<grid, kThreads, smem, st>>>(pd, n, plan_dev + kPlanHeader, plan_dev + kPlanHeader + n + 1, xcap, x_dtype, y_dtype, peers);
     return jq_launch_status();
 }
 
@@ -1192,9 +1265,18 @@ static int launch_grouped(const jq_problem *pd, const int *plan_host, const int 
                           const PeerInfo &peers, cudaStream_t st) {
     if (gemv_smem_bytes<FMT, B, 4>(plan_host[3]) <= kMaxSmem)
         return launch_grouped_d<FMT, B, 4>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
-    if constexpr (Tile<FMT, B>::kMma)
+    if constexpr (Tile<FMT, B>::kMma) {
         if (gemv_smem_bytes<FMT, B, 3>(plan_host[3]) <= kMaxSmem)
             return launch_grouped_d<FMT, B, 3>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
+        // the largest K does not fit even with two stages: K-tiled MMA row loop, three stages, a K tile of at
+        // least 1024 codes and one row group of partial sums must fit
+        if (gemv_smem_bytes<FMT, B, 2>(plan_host[3]) > kMaxSmem) {
+            const long long xcap = ((long long)kMaxSmem - ring_bytes<FMT, B, 3>() - kSmallBytes) / 2;
+            const long long tileK = ((xcap / 2) / B - kXPad) / 1024 * 1024;
+            if (tileK >= 1024 && (xcap - B * (tileK + kXPad) - 8) / 2 / (16 * B) >= 1)
+                return launch_grouped_d<FMT, B, 3>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
+        }
+    }
     return launch_grouped_d<FMT, B, 2>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
 }
 

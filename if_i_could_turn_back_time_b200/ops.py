@@ -19,7 +19,7 @@ from .spec import QuantSpec
 _DT = {torch.float32: _lib.JQ_F32, torch.float16: _lib.JQ_F16, torch.bfloat16: _lib.JQ_BF16}
 MAX_GEMV_BATCH = 8
 MAX_TC_BATCH = 64
-TC_MIN_BATCH = 9          # from here on E2M1 g32 goes to the tensor-core kernel
+TC_MIN_BATCH = 17         # from here on E2M1 g32 goes to the tensor-core kernel (up to 16: two passes of the batch-8 loop are faster)
 _last_tc_workspace = None  # kept for status inspection (ops.tc_status())
 
 
@@ -249,22 +249,29 @@ class GroupedGemv:
             arr[i].ldy = self.full_rows[i]
         self._problems_host = arr
         self._per_problem = False
-        self.launches_per_run = 1
-        if batch > MAX_GEMV_BATCH:
-            # beyond the CUDA-core kernel's batch: one call per matrix (tensor-core path where eligible)
-            if self._symm is not None or any(self.row_offsets):
-                raise ValueError("the fused exchange needs batch <= 8")
-            self._per_problem = True
+        self._subs = []
+        self._use_tc = (self._symm is None and not any(self.row_offsets) and batch <= MAX_TC_BATCH
+                        and all(tc_eligible(w.spec.fmt_id, w.K, w.spec.group_size, batch) for w in weights))
+        if self._use_tc:
             self.launches_per_run = None
             return
+        # one grouped launch per sub-batch of at most 8 rows (the row loops' limit)
         with torch.cuda.device(self.device):
-            nbytes = lib.jq_grouped_plan_bytes(n)
-            self._plan_host = np.zeros((nbytes + 3) // 4, dtype=np.int32)
-            _lib.check(lib.jq_grouped_plan(spec0.fmt_id, ctypes.byref(arr), n, batch, self._plan_host.ctypes.data,
-                                           self._plan_host.nbytes), "jq_grouped_plan")
-            raw = np.frombuffer(bytes(arr), dtype=np.uint8).copy()
-            self._problems_dev = torch.from_numpy(raw).to(self.device)
-            self._plan_dev = torch.from_numpy(self._plan_host).to(self.device)
+            for b0 in range(0, batch, MAX_GEMV_BATCH):
+                nb = min(MAX_GEMV_BATCH, batch - b0)
+                sub = (_lib.jq_problem * n)()
+                ctypes.memmove(sub, arr, ctypes.sizeof(arr))
+                for i, (w, nf) in enumerate(zip(weights, self.full_rows)):
+                    sub[i].x = arr[i].x + b0 * w.K * esz
+                    sub[i].y = arr[i].y + b0 * nf * esz
+                nbytes = lib.jq_grouped_plan_bytes(n)
+                plan_host = np.zeros((nbytes + 3) // 4, dtype=np.int32)
+                _lib.check(lib.jq_grouped_plan(spec0.fmt_id, ctypes.byref(sub), n, nb, plan_host.ctypes.data,
+                                               plan_host.nbytes), "jq_grouped_plan")
+                raw = np.frombuffer(bytes(sub), dtype=np.uint8).copy()
+                self._subs.append((torch.from_numpy(raw).to(self.device), plan_host,
+                                   torch.from_numpy(plan_host).to(self.device)))
+        self.launches_per_run = len(self._subs)
 
     @property
     def fused_exchange(self) -> bool:
@@ -278,11 +285,15 @@ class GroupedGemv:
 
     def run(self) -> None:
         lib = _lib.load()
-        if not self._per_problem:
+        if not self._per_problem and not self._use_tc:
+            st = 0
             with torch.cuda.device(self.device):
-                st = lib.jq_gemv_grouped_peers(_ptr(self._problems_dev), self._plan_host.ctypes.data,
-                                               _ptr(self._plan_dev), _DT[self.x_dtype], _DT[self.x_dtype],
-                                               len(self._peer_delta), self._peer_delta.ctypes.data, _stream())
+                for problems_dev, plan_host, plan_dev in self._subs:
+                    st = lib.jq_gemv_grouped_peers(_ptr(problems_dev), plan_host.ctypes.data, _ptr(plan_dev),
+                                                   _DT[self.x_dtype], _DT[self.x_dtype], len(self._peer_delta),
+                                                   self._peer_delta.ctypes.data, _stream())
+                    if st:
+                        break
             if st != -5:
                 _lib.check(st, "jq_gemv_grouped")
                 return
@@ -290,9 +301,7 @@ class GroupedGemv:
                 _lib.check(st, "jq_gemv_grouped_peers")
             # batch x K too large for one staged activation per CTA: one (split-K) launch per matrix instead
             self._per_problem = True
-        w0 = self.weights[0]
-        if (self.batch <= MAX_TC_BATCH and not any(self.row_offsets)
-                and all(tc_eligible(w.spec.fmt_id, w.K, w.spec.group_size, self.batch) for w in self.weights)):
+        if self._use_tc:
             # every matrix goes to the tensor-core kernel: one host call enqueues them all
             global _last_tc_workspace
             wsb = max(lib.jq_workspace_bytes(1, w.N, w.K, self.batch) for w in self.weights)
@@ -302,7 +311,6 @@ class GroupedGemv:
                                                _DT[self.x_dtype], _DT[self.x_dtype], _ptr(ws), ws.numel(), _stream())
             _lib.check(st, "jq_gemm_e2m1_tc_multi")
             _last_tc_workspace = ws
-            self.launches_per_run = None
             return
         for w, x, y, b, nf, ro in zip(self.weights, self.xs, self.ys, self.biases, self.full_rows, self.row_offsets):
             y[:, ro:ro + w.N].copy_(linear(x, w, b))

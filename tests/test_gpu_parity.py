@@ -260,8 +260,13 @@ def _check_tc(pw, x_cpu, bias_cpu=None):
     x32 = x_cpu.float().numpy()
     b32 = None if bias_cpu is None else bias_cpu.numpy()
     had = bool(pw.spec.had_block)
-    assert ops.tc_eligible(pw.spec.fmt_id, pw.K, pw.spec.group_size, x_cpu.shape[0])
-    y = ops.linear(x_cpu.to(DEV), pwd, None if bias_cpu is None else bias_cpu.to(DEV), out_dtype=torch.float32)
+    keep = ops.TC_MIN_BATCH
+    ops.TC_MIN_BATCH = 9   # the kernel itself takes 9..64 rows; the default routing starts it at 17
+    try:
+        assert ops.tc_eligible(pw.spec.fmt_id, pw.K, pw.spec.group_size, x_cpu.shape[0])
+        y = ops.linear(x_cpu.to(DEV), pwd, None if bias_cpu is None else bias_cpu.to(DEV), out_dtype=torch.float32)
+    finally:
+        ops.TC_MIN_BATCH = keep
     assert ops.tc_status() == 0, "a device-side wait timed out"
     y = y.cpu().numpy()
     ref = formats.linear_ref(x32, w_hat, b32, had_block=pw.spec.had_block)
@@ -332,8 +337,10 @@ def test_grouped_batched_layers_use_one_tensor_core_host_call():
 
 
 # ---------------------------------------------------------------- grouped ----
-@pytest.mark.parametrize("fmt,g,had,B", [("gf4", 128, 128, 1), ("e2m1", 32, 0, 2), ("gf4", 128, 128, 4)])
+@pytest.mark.parametrize("fmt,g,had,B", [("gf4", 128, 128, 1), ("e2m1", 32, 0, 2), ("gf4", 128, 128, 4),
+                                         ("e2m1", 32, 128, 8), ("e2m1", 32, 0, 13), ("gf4", 128, 0, 11)])
 def test_grouped_launch_equals_single_launches(fmt, g, had, B):
+    """Also batches above 8: one grouped launch per sub-batch of at most 8 rows."""
     shapes = [(512, 1024), (96, 2048), (1000, 256), (3, 4096), (777, 1024)]
     pws = [jq.pack_weight(_weights(n, k, n + k), jq.QuantSpec(fmt, g, had)).to(DEV) for n, k in shapes]
     grp = ops.GroupedGemv(pws, B, torch.bfloat16)
@@ -346,6 +353,27 @@ def test_grouped_launch_equals_single_launches(fmt, g, had, B):
     torch.cuda.synchronize()
     for pw, x, y in zip(pws, grp.xs, grp.ys):
         assert torch.equal(y, ops.linear(x, pw))
+
+
+@pytest.mark.parametrize("B,had", [(4, 0), (8, 128), (5, 0)])
+def test_grouped_launch_tiles_k_when_batch_times_k_exceeds_shared_memory(B, had):
+    """B x 28672 fp16 activations do not fit beside the ring: the kernel walks K in tiles and keeps fp32
+    partial sums per row in shared memory (other matrices of the same launch run untiled)."""
+    shapes = [(200, 28672), (48, 8192), (33, 256), (16, 28672)]
+    pws = [jq.pack_weight(_weights(n, k, n + k), jq.QuantSpec("e2m1", 32, had)).to(DEV) for n, k in shapes]
+    gen = torch.Generator("cpu").manual_seed(B)
+    biases = [torch.randn(n, generator=gen).to(DEV) for n, _ in shapes]
+    grp = ops.GroupedGemv(pws, B, torch.float32, biases=biases)
+    for x in grp.xs:
+        x.copy_(torch.randn(x.shape, generator=gen))
+    for y in grp.ys:
+        y.fill_(float("nan"))
+    grp.run()
+    torch.cuda.synchronize()
+    assert grp.launches_per_run == 1
+    for pw, x, y, b in zip(pws, grp.xs, grp.ys, biases):
+        ref = ops.linear(x, pw, b)     # single launches (split-K through a workspace for the long rows)
+        assert formats.rel_err(y.cpu().numpy(), ref.cpu().numpy()) <= 2e-6
 
 
 def test_grouped_row_shards_and_peer_copies_on_one_gpu():
