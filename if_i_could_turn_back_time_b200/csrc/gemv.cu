@@ -992,9 +992,8 @@ static int launch_gemv_d(const GemvProblem &p, int x_dtype, int y_dtype, cudaStr
     auto kern = gemv_kernel<FMT, B, DEPTH>;
     JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int row_groups = (p.N + Tile<FMT, B>::R - 1) / Tile<FMT, B>::R;
-    int grid = jq_sm_count();  // one persistent CTA per SM
-    const int need = (row_groups + kWarps - 1) / kWarps;
-    if (grid > need) grid = need;
+    int grid = jq_sm_count();  // one persistent CTA per SM; a small matrix still spreads over all of them
+    if (grid > row_groups) grid = row_groups;
     kern<<<grid, kThreads, smem, st>>>(p, x_dtype, y_dtype);
     return jq_launch_status();
 }

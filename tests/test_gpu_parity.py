@@ -376,20 +376,22 @@ def test_grouped_launch_tiles_k_when_batch_times_k_exceeds_shared_memory(B, had)
         assert formats.rel_err(y.cpu().numpy(), ref.cpu().numpy()) <= 2e-6
 
 
-def test_grouped_row_shards_and_peer_copies_on_one_gpu():
+@pytest.mark.parametrize("fmt,g,had,B", [("gf4", 128, 128, 1), ("e2m1", 32, 0, 1), ("e2m1", 32, 128, 4),
+                                         ("e2m1", 32, 0, 7)])
+def test_grouped_row_shards_and_peer_copies_on_one_gpu(fmt, g, had, B):
     """Two row shards of each matrix run as two grouped launches into full-width outputs; the second
     launch also writes every result into a second buffer through the peer-copy path (here a local
     buffer stands in for a peer GPU's).  Both must equal the unsharded result bit for bit."""
     shapes = [(512, 1024), (96, 2048), (1000, 256)]
-    spec = jq.QuantSpec("gf4", 128, 128)
+    spec = jq.QuantSpec(fmt, g, had)
     full = [jq.pack_weight(_weights(n, k, n + k), spec) for n, k in shapes]
     gen = torch.Generator("cpu").manual_seed(4)
-    xs = [torch.randn(1, k, generator=gen).bfloat16() for _, k in shapes]
+    xs = [torch.randn(B, k, generator=gen).bfloat16() for _, k in shapes]
     ref = [ops.linear(x.to(DEV), pw.to(DEV)) for x, pw in zip(xs, full)]
     halves = []
     for rank in range(2):
         shards = [pw.rows(rank * pw.N // 2, (rank + 1) * pw.N // 2).to(DEV) for pw in full]
-        grp = ops.GroupedGemv(shards, 1, torch.bfloat16, full_rows=[pw.N for pw in full],
+        grp = ops.GroupedGemv(shards, B, torch.bfloat16, full_rows=[pw.N for pw in full],
                               row_offsets=[rank * pw.N // 2 for pw in full])
         for gx, x in zip(grp.xs, xs):
             gx.copy_(x)
@@ -407,8 +409,8 @@ def test_grouped_row_shards_and_peer_copies_on_one_gpu():
         assert torch.equal(halves[1].ys[i][:, lo:], r[:, lo:])
     esz = 2
     for i, (o, pw) in enumerate(zip(halves[0].y_offsets, full)):
-        got = mirror[o:o + pw.N * esz].view(torch.bfloat16)[: pw.N // 2]
-        assert torch.equal(got, ref[i][0, : pw.N // 2])             # rank 0's half also landed in the mirror
+        got = mirror[o:o + B * pw.N * esz].view(torch.bfloat16).view(B, pw.N)[:, : pw.N // 2]
+        assert torch.equal(got, ref[i][:, : pw.N // 2])             # rank 0's half also landed in the mirror
 
 
 # ----------------------------------------------------------------- conv2d ----
