@@ -102,7 +102,10 @@ int jq_fwht_block(const void *x, float *y, int B, int K, int block, int x_dtype,
  * [B,N] of y_dtype, bias fp32 [N] or NULL.  had_block is 0 (no rotation) or
  * 128 (K % 128 == 0).  The rotated activation is rounded to fp16 after an
  * exact power-of-two normalisation per batch row; products are exact and
- * accumulated in fp32.  workspace may be NULL when jq_workspace_bytes says 0. */
+ * accumulated in fp32 (batch 1 and GF4: fma.rn.f32.f16 on the CUDA cores; E2M1
+ * with 32-code groups, K % 256 == 0 and 2 <= B <= 8: the same products on
+ * mma.sync.m16n8k16, one instruction per 256 codes whatever B).  workspace may
+ * be NULL when jq_workspace_bytes says 0. */
 int jq_gemv_e2m1(const void *qweight, const void *scales, const void *x,
                  const float *bias_or_null, void *y, int N, int K, int B, int g,
                  int had_block, int x_dtype, int y_dtype, void *workspace,
