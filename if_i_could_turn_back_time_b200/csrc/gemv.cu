@@ -1259,6 +1259,9 @@ static int launch_grouped_d(const jq_problem *pd, const int *plan_host, const in
     return jq_launch_status();
 }
 
+#ifndef JQ_TILED_DEPTH
+#define JQ_TILED_DEPTH(B) 2   // stages of the ring in a K-tiled launch: larger K tiles beat a deeper ring (decode70b, batch 8: 1142 vs 888 tok/s)
+#endif
 template <int FMT, int B>
 static int launch_grouped(const jq_problem *pd, const int *plan_host, const int *plan_dev, int x_dtype, int y_dtype,
                           const PeerInfo &peers, cudaStream_t st) {
@@ -1267,13 +1270,17 @@ static int launch_grouped(const jq_problem *pd, const int *plan_host, const int 
     if constexpr (Tile<FMT, B>::kMma) {
         if (gemv_smem_bytes<FMT, B, 3>(plan_host[3]) <= kMaxSmem)
             return launch_grouped_d<FMT, B, 3>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
-        // the largest K does not fit even with two stages: K-tiled MMA row loop, three stages, a K tile of at
-        // least 1024 codes and one row group of partial sums must fit
+        // the largest K does not fit even with two stages: K-tiled MMA row loop, if a K tile of
+        // at least 1024 codes and one row group of partial sums fit and every problem that cannot be tiled fits
+        // whole.  (Where two stages untiled fit they are faster than three stages tiled: 3.6 vs 3.1 TB/s at
+        // 16 x 8192 x 8192, batch 8.)
         if (gemv_smem_bytes<FMT, B, 2>(plan_host[3]) > kMaxSmem) {
-            const long long xcap = ((long long)kMaxSmem - ring_bytes<FMT, B, 3>() - kSmallBytes) / 2;
+            constexpr int TD = JQ_TILED_DEPTH(B);
+            const long long xcap = ((long long)kMaxSmem - ring_bytes<FMT, B, TD>() - kSmallBytes) / 2;
             const long long tileK = ((xcap / 2) / B - kXPad) / 1024 * 1024;
-            if (tileK >= 1024 && (xcap - B * (tileK + kXPad) - 8) / 2 / (16 * B) >= 1)
-                return launch_grouped_d<FMT, B, 3>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
+            if (tileK >= 1024 && (xcap - B * (tileK + kXPad) - 8) / 2 / (16 * B) >= 1 &&
+                gemv_smem_bytes<FMT, B, TD>(plan_host[7]) <= kMaxSmem)
+                return launch_grouped_d<FMT, B, TD>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
         }
     }
     return launch_grouped_d<FMT, B, 2>(pd, plan_host, plan_dev, x_dtype, y_dtype, peers, st);
