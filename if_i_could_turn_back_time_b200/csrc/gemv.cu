@@ -54,6 +54,9 @@ constexpr int kWarps = kThreads / 32;
 #ifndef JQ_T_GF4
 #define JQ_T_GF4 4
 #endif
+#ifndef JQ_MMA_MINB_GF4
+#define JQ_MMA_MINB_GF4 3
+#endif
 #ifndef JQ_MMA_MINB
 #define JQ_MMA_MINB 2   // E2M1 batches from here up to 8 use the m16n8k16 row loop when the problem allows
 #endif
@@ -61,7 +64,8 @@ template <int FMT, int B>
 struct Tile {
     // rows a warp carries at once in the FMA row loops; bounded by registers and by the ring's shared memory
     static constexpr int T = (B <= 2) ? (FMT == JQ_FMT_GF4 ? JQ_T_GF4 : JQ_T_E2M1) : (B <= 4 ? 2 : 1);
-    static constexpr bool kMma = FMT == JQ_FMT_E2M1 && B >= JQ_MMA_MINB;
+    // both formats have an MMA row loop for batches (GF4 from 3 rows: at 2 the FMA loop's shared tables are faster)
+    static constexpr bool kMma = B >= (FMT == JQ_FMT_GF4 ? JQ_MMA_MINB_GF4 : JQ_MMA_MINB);
     // rows of a row group, the unit in which work is handed to warps (and planned on the host)
     static constexpr int R = kMma ? 16 : T;
 };
@@ -615,10 +619,26 @@ struct MmaRing {
     static constexpr int kBytes = kWarps * DEPTH * kMmaStageBytes + kCombBytes + 128;  // + slack to start at a 128-byte boundary
 };
 
-// The problem suits the MMA row loop: one scale per 32-code chunk, whole
-// 8-chunk stages, 16-byte aligned scale rows.
+// GF4: the same slots, plus 2 KB of lookup table per warp (two warps share a
+// 4 KB aligned block, see cta_rows_mma_gf4).
+template <int DEPTH>
+struct MmaRingGf4 {
+    static constexpr int kTabBytes = (kWarps / 2) * 4096 + 4096;   // + slack to start at a 4 KB boundary
+    static constexpr int kBytes = MmaRing<DEPTH>::kBytes + kTabBytes;
+};
+
+// The problem suits the MMA row loop.  E2M1: one scale per 32-code chunk, whole
+// 8-chunk stages, 16-byte aligned scale rows.  GF4: 128-code groups (two per
+// stage and row, copied as one aligned fp16 pair), 16-byte aligned codebooks.
+template <int FMT>
+__host__ __device__ inline bool mma_ok_raw(int g, int K, const void *scales, const void *codebook) {
+    if (FMT == JQ_FMT_E2M1) return g == 32 && (K & 255) == 0 && (reinterpret_cast<uintptr_t>(scales) & 15u) == 0;
+    return g == 128 && (K & 255) == 0 && (reinterpret_cast<uintptr_t>(scales) & 3u) == 0 &&
+           (reinterpret_cast<uintptr_t>(codebook) & 15u) == 0;
+}
+template <int FMT>
 __device__ __forceinline__ bool mma_ok(const GemvProblem &p) {
-    return p.g == 32 && (p.K & 255) == 0 && (p.lds & 7) == 0 && (reinterpret_cast<uintptr_t>(p.scales) & 15u) == 0;
+    return mma_ok_raw<FMT>(p.g, p.K, p.scales, p.codebook) && (FMT == JQ_FMT_E2M1 ? (p.lds & 7) == 0 : (p.lds & 1) == 0);
 }
 
 // K parts a row group is cut into (a function of K alone, so that every launch
@@ -635,6 +655,69 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
     asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+// End of a task of the MMA row loops.  acc = this K part's sums of rows g, g + 8
+// x batch columns 2t, 2t + 1 (g = lane / 4, t = lane % 4).  The parts of a row
+// group are joined in part order, then the first part's warp writes the outputs
+// (or, in a K-tiled launch, adds them to the chunk's table in shared memory).
+template <int B>
+__device__ __forceinline__ void mma_task_end(const GemvProblem &p, float (&acc)[4], int ctask, int ksh, int &cpar,
+                                             float4 *comb, const int *sexp, int y_dtype, float *partial,
+                                             int partial_rg0, bool partial_first) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int ks = 1 << ksh, N = p.N;
+    // acc = this K part's sums of rows g, g + 8 x batch columns 2t, 2t + 1
+    bool writer = true;
+    if (ks > 1) {
+        // the parts of a row group sit on ks adjacent warps in the same round: all but the first
+        // park their sums in shared memory (two alternating sets, so that a set is never rewritten
+        // before its reader has passed the next round's barrier), the first adds them in part order
+        writer = (warp & (ks - 1)) == 0;
+        float4 *mine = comb + (cpar * kWarps + warp) * 32 + lane;
+        if (!writer) *mine = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + (warp >> ksh)), "r"(ks * 32) : "memory");
+        if (writer) {
+            for (int q = 1; q < ks; ++q) {
+                const float4 o = mine[q * 32];
+                acc[0] += o.x; acc[1] += o.y; acc[2] += o.z; acc[3] += o.w;
+            }
+        }
+        cpar ^= 1;
+    }
+    if (writer && partial) {
+        // one K tile of several: the sums go to the chunk's [row][batch] table in shared memory
+        const int rg = ctask >> ksh;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int b = 2 * t + j;
+                if (b < B) {
+                    float *dst = partial + ((rg - partial_rg0) * 16 + g + 8 * h) * B + b;
+                    *dst = partial_first ? acc[2 * h + j] : *dst + acc[2 * h + j];
+                }
+            }
+    } else if (writer) {
+        const int rg = ctask >> ksh;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = rg * 16 + g + 8 * h;
+            if (row < N) {
+                const float bias = p.bias ? p.bias[row] : 0.f;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int b = 2 * t + j;
+                    if (b < B) {
+                        const float up = __uint_as_float((uint32_t)(127 + sexp[b]) << 23);  // 2^e
+                        const float v = fmaf(acc[2 * h + j], up, bias);
+                        for (int cpy = 0; cpy < p.npeer; ++cpy)
+                            store_out(reinterpret_cast<char *>(p.y) + p.peer_delta[cpy], (size_t)b * p.ldy + row, v, y_dtype);
+                    }
+                }
+            }
+        }
+    }
 }
 
 template <int B, int DEPTH>
@@ -735,57 +818,166 @@ __device__ void cta_rows_mma(const GemvProblem &p, int rg_lo, int rg_hi, const _
         }
         cslot = (cslot + 1 == DEPTH) ? 0 : cslot + 1;
         if (++ci == nitp) {
-            // acc = this K part's sums of rows g, g + 8 x batch columns 2t, 2t + 1
-            bool writer = true;
-            if (ks > 1) {
-                // the parts of a row group sit on ks adjacent warps in the same round: all but the first
-                // park their sums in shared memory (two alternating sets, so that a set is never rewritten
-                // before its reader has passed the next round's barrier), the first adds them in part order
-                writer = (warp & (ks - 1)) == 0;
-                float4 *mine = comb + (cpar * kWarps + warp) * 32 + lane;
-                if (!writer) *mine = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                asm volatile("bar.sync %0, %1;" ::"r"(1 + (warp >> ksh)), "r"(ks * 32) : "memory");
-                if (writer) {
-                    for (int q = 1; q < ks; ++q) {
-                        const float4 o = mine[q * 32];
-                        acc[0] += o.x; acc[1] += o.y; acc[2] += o.z; acc[3] += o.w;
-                    }
+            mma_task_end<B>(p, acc, ctask, ksh, cpar, comb, sexp, y_dtype, partial, partial_rg0, partial_first);
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+            ci = 0;
+            ctask += kWarps;
+        }
+    }
+    cp_async_wait<0>();
+}
+
+// ---- GF4, batch 2..8: table lookups feeding mma.sync.m16n8k16 --------------------
+// Same tasks, ring, fragments and task end as cta_rows_mma; what differs is the
+// decode.  In the MMA layout the 32 lanes of a lookup instruction belong to 8
+// different rows, so a shared 32-byte table per row would collide in the banks.
+// Instead every lane owns one 4-byte column of a [16 entries][32 lanes] table:
+// the word of entry e holds {codebook[row g][e], codebook[row g + 8][e]} of the
+// lane's own two rows (the 4 lanes of a row hold identical copies).  A lookup
+// never leaves the lane's own bank: conflict-free whatever the codes.  Entries
+// are 256 bytes apart (two warps interleave their 128-byte halves in a 4 KB
+// aligned block), so the entry index is bits 8..11 of the address and one PRMT
+// splices a nibble (OR-ed with the block's address bits 12..15) into byte 1.
+// The table is rebuilt per task from codebook rows prefetched into registers a
+// task ahead.  Group scales (128 codes = 4 chunks) are applied after four
+// chunks' MMAs, not after each.
+__device__ __forceinline__ void gf4_lookup8(uint32_t w, uint32_t tb, uint32_t hb4, uint32_t (&h)[4]) {
+    uint32_t m0, m1;  // bytes: nibbles {0,2,4,6} | hb  and  nibbles {1,3,5,7} | hb
+    asm("lop3.b32 %0, %1, 0x0f0f0f0f, %2, 0xea;" : "=r"(m0) : "r"(w), "r"(hb4));       // (a & b) | c
+    asm("lop3.b32 %0, %1, 0x0f0f0f0f, %2, 0xea;" : "=r"(m1) : "r"(w >> 4), "r"(hb4));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t a0 = __byte_perm(m0, tb, 0x7604 | (j << 4)), a1 = __byte_perm(m1, tb, 0x7604 | (j << 4));
+        uint32_t v0, v1;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v0) : "r"(a0));
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v1) : "r"(a1));
+        asm("mad.lo.u32 %0, %1, 65536, %2;" : "=r"(h[j]) : "r"(v1), "r"(v0));   // pack on the FMA pipe
+    }
+}
+
+template <int B, int DEPTH>
+__device__ void cta_rows_mma_gf4(const GemvProblem &p, int rg_lo, int rg_hi, const __half *xs, const int *sexp,
+                                 unsigned char *ring_base, int y_dtype, float *partial = nullptr, int partial_rg0 = 0,
+                                 bool partial_first = true) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int N = p.N, XSB = xs_halves(p.K) + kXPad;
+    const int nit = p.K >> 8;                            // stages (8 chunks of 32 codes = 2 scale groups) per row
+    const uint32_t ring = ((smem_u32(ring_base) + 127u) & ~127u) + warp * (DEPTH * kMmaStageBytes);
+    const int prow = lane >> 3, pch = lane & 7;
+    const uint32_t cw = ring + g * 128 + (g << 4) + t * 4;           // ^ (c << 4); + 1024 for row g + 8
+    const uint32_t cs = ring + 2048 + g * 4;                         // scale pair of row g; + 32 for row g + 8
+    const uint32_t xs_u = smem_u32(xs) + (uint32_t)(min(g, B - 1) * XSB + t * 8) * 2;
+    float4 *comb = reinterpret_cast<float4 *>(ring_base + (MmaRing<DEPTH>::kBytes - MmaRing<DEPTH>::kCombBytes));
+    // this lane's table column: entry e at tcol + 256 e, row g in the low half, row g + 8 in the high half
+    const uint32_t tcol = ((smem_u32(ring_base) + MmaRing<DEPTH>::kBytes + 4095u) & ~4095u) + (warp >> 1) * 4096 +
+                          (warp & 1) * 128 + lane * 4;
+    const uint32_t hb4 = ((tcol >> 8) & 0xf0u) * 0x01010101u;
+
+    const int ksh = mma_ksplit_log2(p.K), ks = 1 << ksh, nitp = nit >> ksh;
+    const int first = (rg_lo << ksh) + warp, task_end = rg_hi << ksh;
+    const int ntask = first < task_end ? (task_end - first + kWarps - 1) / kWarps : 0;
+    const int total = ntask * nitp;
+
+    // ---- producer state ----
+    int is = 0, ii = 0, itask = first, islot = 0;
+    const uint8_t *wptr[4];
+    const __half *sptr = nullptr;
+    auto issue = [&]() {
+        if (is < total) {
+            if (ii == 0) {
+                const int rg = itask >> ksh, part = itask & (ks - 1);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = min(rg * 16 + 4 * i + prow, N - 1);
+                    wptr[i] = p.qw + (size_t)row * p.ldw + (part * nitp * 8 + pch) * 16;
                 }
-                cpar ^= 1;
+                sptr = p.scales + (size_t)min(rg * 16 + (lane & 15), N - 1) * p.lds + part * nitp * 2;
             }
-            if (writer && partial) {
-                // one K tile of several: the sums go to the chunk's [row][batch] table in shared memory
-                const int rg = ctask >> ksh;
+            const uint32_t slot = islot * kMmaStageBytes;
 #pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const int b = 2 * t + j;
-                        if (b < B) {
-                            float *dst = partial + ((rg - partial_rg0) * 16 + g + 8 * h) * B + b;
-                            *dst = partial_first ? acc[2 * h + j] : *dst + acc[2 * h + j];
-                        }
-                    }
-            } else if (writer) {
-                const int rg = ctask >> ksh;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int row = rg * 16 + g + 8 * h;
-                    if (row < N) {
-                        const float bias = p.bias ? p.bias[row] : 0.f;
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-                            const int b = 2 * t + j;
-                            if (b < B) {
-                                const float up = __uint_as_float((uint32_t)(127 + sexp[b]) << 23);  // 2^e
-                                const float v = fmaf(acc[2 * h + j], up, bias);
-                                for (int cpy = 0; cpy < p.npeer; ++cpy)
-                                    store_out(reinterpret_cast<char *>(p.y) + p.peer_delta[cpy], (size_t)b * p.ldy + row, v, y_dtype);
-                            }
-                        }
-                    }
-                }
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t key = (uint32_t)((4 * i + prow) & 7);
+                cp_async16(ring + slot + (4 * i + prow) * 128 + ((pch ^ key) << 4), wptr[i]);
+                wptr[i] += 128;
             }
+            if (lane < 16) cp_async4(ring + slot + 2048 + lane * 4, sptr);
+            sptr += 2;
+            if (++ii == nitp) { ii = 0; itask += kWarps; }
+        }
+        ++is;
+        islot = (islot + 1 == DEPTH) ? 0 : islot + 1;
+        cp_async_commit();
+    };
+
+    // codebook rows g and g + 8 of a task's row group, as 2 x 2 16-byte halves
+    uint4 cb[4];
+    auto fetch_tables = [&](int task) {
+        if (task < task_end) {
+            const int rg = task >> ksh;
+            const uint4 *ra = reinterpret_cast<const uint4 *>(p.codebook + (size_t)min(rg * 16 + g, N - 1) * 16);
+            const uint4 *rb = reinterpret_cast<const uint4 *>(p.codebook + (size_t)min(rg * 16 + g + 8, N - 1) * 16);
+            cb[0] = __ldg(ra); cb[1] = __ldg(ra + 1); cb[2] = __ldg(rb); cb[3] = __ldg(rb + 1);
+        }
+    };
+    auto build_tables = [&]() {
+        const uint32_t a[8] = {cb[0].x, cb[0].y, cb[0].z, cb[0].w, cb[1].x, cb[1].y, cb[1].z, cb[1].w};
+        const uint32_t b[8] = {cb[2].x, cb[2].y, cb[2].z, cb[2].w, cb[3].x, cb[3].y, cb[3].z, cb[3].w};
+#pragma unroll
+        for (int e2 = 0; e2 < 8; ++e2) {
+            // entries 2 e2 and 2 e2 + 1: {row g, row g + 8} pairs
+            const uint32_t lo = __byte_perm(a[e2], b[e2], 0x5410), hi = __byte_perm(a[e2], b[e2], 0x7632);
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(tcol + (2 * e2) * 256), "r"(lo) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(tcol + (2 * e2 + 1) * 256), "r"(hi) : "memory");
+        }
+    };
+
+#pragma unroll
+    for (int d = 0; d < DEPTH - 1; ++d) issue();
+    fetch_tables(first);
+
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+    int ci = 0, ctask = first, cslot = 0, cpar = 0;
+    for (int s = 0; s < total; ++s) {
+        if (ci == 0) {
+            build_tables();                    // own column only: no other lane reads it
+            fetch_tables(ctask + kWarps);      // the next task's rows, in flight during this task
+        }
+        cp_async_wait<DEPTH - 2>();   // this thread's copies of stage s have landed
+        __syncwarp();                 // ... and everyone's; everyone has also finished reading stage s - 1
+        issue();                      // refills the slot of stage s - 1
+        const uint32_t slot = cslot * kMmaStageBytes;
+        const uint32_t pa = lds32(cs + slot), pb = lds32(cs + slot + 32);   // 2 scales of rows g and g + 8
+        const float2 fa = __half22float2(*reinterpret_cast<const __half2 *>(&pa));
+        const float2 fb = __half22float2(*reinterpret_cast<const __half2 *>(&pb));
+        const uint32_t xbase = xs_u + (uint32_t)(((ctask & (ks - 1)) * nitp + ci) * 256) * 2;
+        const uint32_t cwslot = cw + slot;
+#pragma unroll
+        for (int hs = 0; hs < 2; ++hs) {       // the stage's two scale groups
+            float d[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = 4 * hs + j;
+                const uint32_t a = cwslot ^ (uint32_t)(c << 4);
+                const uint32_t wa = lds32(a), wb = lds32(a + 1024);
+                const uint4 xv = lds128(xbase + c * 64);
+                uint32_t ha[4], hb[4];
+                gf4_lookup8(wa, tcol, hb4, ha);
+                gf4_lookup8(wb, tcol + 2, hb4, hb);
+                if (j == 0) mma16816(d, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y, zero);
+                else mma16816(d, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y, d);
+                mma16816(d, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w, d);
+            }
+            const float sca = hs ? fa.y : fa.x, scb = hs ? fb.y : fb.x;
+            acc[0] = fmaf(d[0], sca, acc[0]);
+            acc[1] = fmaf(d[1], sca, acc[1]);
+            acc[2] = fmaf(d[2], scb, acc[2]);
+            acc[3] = fmaf(d[3], scb, acc[3]);
+        }
+        cslot = (cslot + 1 == DEPTH) ? 0 : cslot + 1;
+        if (++ci == nitp) {
+            mma_task_end<B>(p, acc, ctask, ksh, cpar, comb, sexp, y_dtype, partial, partial_rg0, partial_first);
             acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
             ci = 0;
             ctask += kWarps;
@@ -802,8 +994,9 @@ template <int FMT, int B, int DEPTH>
 __device__ __forceinline__ void run_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __half *xs, const int *sexp,
                                          unsigned char *ring_base, int y_dtype) {
     if constexpr (Tile<FMT, B>::kMma) {
-        if (mma_ok(p)) {
-            cta_rows_mma<B, DEPTH>(p, rg_lo, rg_hi, xs, sexp, ring_base, y_dtype);
+        if (mma_ok<FMT>(p)) {
+            if constexpr (FMT == JQ_FMT_GF4) cta_rows_mma_gf4<B, DEPTH>(p, rg_lo, rg_hi, xs, sexp, ring_base, y_dtype);
+            else cta_rows_mma<B, DEPTH>(p, rg_lo, rg_hi, xs, sexp, ring_base, y_dtype);
             return;
         }
     }
@@ -825,8 +1018,8 @@ __device__ __forceinline__ void run_rows(const GemvProblem &p, int rg_lo, int rg
 // the wider activation rows
 template <int FMT, int B, int DEPTH>
 __host__ __device__ constexpr int ring_bytes() {
-    return (Tile<FMT, B>::kMma && MmaRing<DEPTH>::kBytes > Ring<FMT, B, DEPTH>::kBytes) ? MmaRing<DEPTH>::kBytes
-                                                                                     : Ring<FMT, B, DEPTH>::kBytes;
+    constexpr int mma = FMT == JQ_FMT_GF4 ? MmaRingGf4<DEPTH>::kBytes : MmaRing<DEPTH>::kBytes;
+    return (Tile<FMT, B>::kMma && mma > Ring<FMT, B, DEPTH>::kBytes) ? mma : Ring<FMT, B, DEPTH>::kBytes;
 }
 template <int FMT, int B>
 __host__ __device__ inline int xs_stride(int K) { return xs_halves(K) + (Tile<FMT, B>::kMma ? kXPad : 0); }
@@ -855,7 +1048,7 @@ __device__ __forceinline__ SmemLayout carve(unsigned char *smem) {
 // sums (fp32, [row][batch]) live in the rest and are turned into outputs after
 // the last tile.  The normalisation exponent is that of the whole row, so the
 // tiles add up in one scale.
-template <int B, int DEPTH>
+template <int FMT, int B, int DEPTH>
 __device__ void rows_k_tiled(const GemvProblem &p, int rg_lo, int rg_hi, const SmemLayout &L, int xcap, int x_dtype,
                              int y_dtype) {
     const int tileK = ((xcap / 2) / B - kXPad) / 1024 * 1024;
@@ -870,11 +1063,14 @@ __device__ void rows_k_tiled(const GemvProblem &p, int rg_lo, int rg_hi, const S
             GemvProblem q = p;
             q.K = min(tileK, p.K - k0);
             q.qw = p.qw + (k0 >> 1);
-            q.scales = p.scales + (k0 >> 5);
+            q.scales = p.scales + k0 / p.g;
             q.x = reinterpret_cast<const char *>(p.x) + (size_t)k0 * xe;
             __syncthreads();  // the previous tile's activation is no longer read
             stage_activation<B>(q, x_dtype, L.xs, L.sred, L.sexp, true, !(c0 == rg_lo && k0 == 0));
-            cta_rows_mma<B, DEPTH>(q, c0, c1, L.xs, L.sexp, L.ring, y_dtype, partial, c0, k0 == 0);
+            if constexpr (FMT == JQ_FMT_GF4)
+                cta_rows_mma_gf4<B, DEPTH>(q, c0, c1, L.xs, L.sexp, L.ring, y_dtype, partial, c0, k0 == 0);
+            else
+                cta_rows_mma<B, DEPTH>(q, c0, c1, L.xs, L.sexp, L.ring, y_dtype, partial, c0, k0 == 0);
         }
         __syncthreads();
         for (int i = threadIdx.x; i < (c1 - c0) * 16 * B; i += kThreads) {
@@ -893,7 +1089,7 @@ template <int FMT, int B, int DEPTH>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvProblem p, int x_dtype, int y_dtype) {
     extern __shared__ __align__(16) unsigned char smem[];
     const SmemLayout L = carve<FMT, B, DEPTH>(smem);
-    stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp, Tile<FMT, B>::kMma && mma_ok(p));
+    stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp, Tile<FMT, B>::kMma && mma_ok<FMT>(p));
     constexpr int T = Tile<FMT, B>::R;
     const long long nrg = (p.N + T - 1) / T;
     const int lo = (int)(nrg * blockIdx.x / gridDim.x), hi = (int)(nrg * (blockIdx.x + 1) / gridDim.x);
@@ -944,12 +1140,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_prob
         const int base = rg_start[pi];
         const int lim = min(rg_end, rg_start[pi + 1]);
         bool tiled = false;
-        if constexpr (Tile<FMT, B>::kMma) tiled = B * xs_stride<FMT, B>(p.K) > xcap && mma_ok(p);
+        if constexpr (Tile<FMT, B>::kMma) tiled = B * xs_stride<FMT, B>(p.K) > xcap && mma_ok<FMT>(p);
         if (!tiled) {
-            stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp, Tile<FMT, B>::kMma && mma_ok(p));
+            stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp, Tile<FMT, B>::kMma && mma_ok<FMT>(p));
             run_rows<FMT, B, DEPTH>(p, rg - base, lim - base, L.xs, L.sexp, L.ring, y_dtype);
         } else if constexpr (Tile<FMT, B>::kMma) {
-            rows_k_tiled<B, DEPTH>(p, rg - base, lim - base, L, xcap, x_dtype, y_dtype);
+            rows_k_tiled<FMT, B, DEPTH>(p, rg - base, lim - base, L, xcap, x_dtype, y_dtype);
         }
         rg = lim;
         __syncthreads();  // all warps done with xs before the next problem restages it
@@ -1197,7 +1393,7 @@ extern "C" int jq_grouped_plan(int fmt, const jq_problem *ph, int n, int B, void
     int maxK = 0, maxK_whole = 0;
     double total = 0;
     rg_start[0] = 0;
-    const bool mma_fmt = fmt == JQ_FMT_E2M1 && B >= JQ_MMA_MINB;
+    const bool mma_fmt = B >= (fmt == JQ_FMT_GF4 ? JQ_MMA_MINB_GF4 : JQ_MMA_MINB);
     for (int i = 0; i < n; ++i) {
         int st = validate_problem(fmt, ph[i].qweight, ph[i].scales, ph[i].codebook, ph[i].x, ph[i].y, ph[i].N,
                                   ph[i].K, ph[i].g, ph[i].had_block);
@@ -1207,8 +1403,9 @@ extern "C" int jq_grouped_plan(int fmt, const jq_problem *ph, int n, int B, void
         rg_start[i + 1] = rg_start[i] + (int)groups;
         total += (double)groups * ph[i].K;
         maxK = ph[i].K > maxK ? ph[i].K : maxK;
-        const bool tileable = mma_fmt && ph[i].g == 32 && (ph[i].K & 255) == 0 &&
-                              (reinterpret_cast<uintptr_t>(ph[i].scales) & 15u) == 0;  // = mma_ok() on the device
+        const bool tileable = mma_fmt && (fmt == JQ_FMT_E2M1
+                                              ? mma_ok_raw<JQ_FMT_E2M1>(ph[i].g, ph[i].K, ph[i].scales, ph[i].codebook)
+                                              : mma_ok_raw<JQ_FMT_GF4>(ph[i].g, ph[i].K, ph[i].scales, ph[i].codebook));
         if (!tileable && ph[i].K > maxK_whole) maxK_whole = ph[i].K;
     }
     // contiguous CTA ranges of (nearly) equal packed bytes: cut every total/grid

@@ -126,6 +126,36 @@ def test_e2m1_batched_rows_on_the_mma_loop(N, K, had, B):
     _check_gemv(pw, torch.randn(B, K, generator=gen).bfloat16(), torch.randn(N, generator=gen))
 
 
+@pytest.mark.parametrize("N,K,had", [(16, 256, 0), (5, 256, 128), (203, 1024, 128), (48, 2048, 0), (33, 11008, 128),
+                                     (1000, 4096, 128)])
+@pytest.mark.parametrize("B", [2, 3, 7, 8])
+def test_gf4_batched_rows_on_the_mma_loop(N, K, had, B):
+    """GF4 g128, K a multiple of 256, batch 2..8: per-lane table columns feeding the m16n8k16 row loop."""
+    pw = jq.pack_weight(_weights(N, K, N + 5 * K), jq.QuantSpec("gf4", 128, had))
+    gen = torch.Generator("cpu").manual_seed(N + B)
+    _check_gemv(pw, torch.randn(B, K, generator=gen).bfloat16(), torch.randn(N, generator=gen))
+    # a row shard sums in the same order as the whole matrix
+    if N >= 48:
+        pwd = pw.to(DEV)
+        x = torch.randn(B, K, generator=gen).bfloat16().to(DEV)
+        y = ops.linear(x, pwd, out_dtype=torch.float32)
+        assert torch.equal(ops.linear(x, pwd.rows(16, 48), out_dtype=torch.float32), y[:, 16:48])
+
+
+def test_gf4_grouped_launch_tiles_k():
+    shapes = [(200, 11008), (64, 4096), (33, 256)]
+    pws = [jq.pack_weight(_weights(n, k, n + k), jq.QuantSpec("gf4", 128, 128)).to(DEV) for n, k in shapes]
+    gen = torch.Generator("cpu").manual_seed(3)
+    grp = ops.GroupedGemv(pws, 8, torch.float32)
+    for x in grp.xs:
+        x.copy_(torch.randn(x.shape, generator=gen))
+    grp.run()
+    torch.cuda.synchronize()
+    assert grp.launches_per_run == 1
+    for pw, x, y in zip(pws, grp.xs, grp.ys):
+        assert formats.rel_err(y.cpu().numpy(), ops.linear(x, pw).cpu().numpy()) <= 2e-6
+
+
 def test_e2m1_batched_fallbacks_and_row_shards_agree_bit_for_bit():
     gen = torch.Generator("cpu").manual_seed(9)
     # not eligible for the MMA loop (K % 256 != 0, or 64-code groups): the FMA loops take them
@@ -377,7 +407,7 @@ def test_grouped_launch_tiles_k_when_batch_times_k_exceeds_shared_memory(B, had)
 
 
 @pytest.mark.parametrize("fmt,g,had,B", [("gf4", 128, 128, 1), ("e2m1", 32, 0, 1), ("e2m1", 32, 128, 4),
-                                         ("e2m1", 32, 0, 7)])
+                                         ("e2m1", 32, 0, 7), ("gf4", 128, 128, 5)])
 def test_grouped_row_shards_and_peer_copies_on_one_gpu(fmt, g, had, B):
     """Two row shards of each matrix run as two grouped launches into full-width outputs; the second
     launch also writes every result into a second buffer through the peer-copy path (here a local
