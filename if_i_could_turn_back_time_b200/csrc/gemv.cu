@@ -1031,14 +1031,17 @@ struct SmemLayout {
     unsigned char *ring;
 };
 
-constexpr int kSmallBytes = kWarps * 4 + 8 * 4;  // reduction scratch + exponents
+constexpr int kSmallBytes = 128;  // reduction scratch (kWarps floats) + exponents (8 ints), with padding
+// xhalves: halves of the activation region (the small arrays sit behind it)
 template <int FMT, int B, int DEPTH>
-__device__ __forceinline__ SmemLayout carve(unsigned char *smem) {
+__device__ __forceinline__ SmemLayout carve(unsigned char *smem, int xhalves) {
     SmemLayout L;
     L.ring = smem;  // 16-byte aligned slots first
-    L.sred = reinterpret_cast<float *>(smem + ring_bytes<FMT, B, DEPTH>());
+    // (the activation directly behind the ring: with the small arrays in between the GF4 batch-1 loop
+    // measured 3.5 % slower)
+    L.xs = reinterpret_cast<__half *>(smem + ring_bytes<FMT, B, DEPTH>());
+    L.sred = reinterpret_cast<float *>(L.xs + ((xhalves + 7) & ~7));
     L.sexp = reinterpret_cast<int *>(L.sred + kWarps);
-    L.xs = reinterpret_cast<__half *>(L.sexp + 8);  // the staged activation takes the rest
     return L;
 }
 
@@ -1088,7 +1091,7 @@ __device__ void rows_k_tiled(const GemvProblem &p, int rg_lo, int rg_hi, const S
 template <int FMT, int B, int DEPTH>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvProblem p, int x_dtype, int y_dtype) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const SmemLayout L = carve<FMT, B, DEPTH>(smem);
+    const SmemLayout L = carve<FMT, B, DEPTH>(smem, B * xs_stride<FMT, B>(p.K));
     stage_activation<B>(p, x_dtype, L.xs, L.sred, L.sexp, Tile<FMT, B>::kMma && mma_ok<FMT>(p));
     constexpr int T = Tile<FMT, B>::R;
     const long long nrg = (p.N + T - 1) / T;
@@ -1113,7 +1116,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_prob
                                                                      int xcap, int x_dtype, int y_dtype, PeerInfo peers) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int s_prob;
-    const SmemLayout L = carve<FMT, B, DEPTH>(smem);
+    const SmemLayout L = carve<FMT, B, DEPTH>(smem, xcap);
     int rg = cta_first[blockIdx.x];
     const int rg_end = cta_first[blockIdx.x + 1];
     int pi = 0;

@@ -109,32 +109,58 @@ def _linear_rows_tc(x2, qweight, scales, bias, N, K, had, y):
     return y
 
 
+_wsb_cache = {}
+
+
+class _NoDeviceSwitch:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoDeviceSwitch()
+
+
+def _on(device):
+    """Device guard that costs nothing when the tensor's device is already current."""
+    return _NO_SWITCH if device.index == torch.cuda.current_device() else torch.cuda.device(device)
+
+
 def _linear_rows(x2, qweight, scales, codebook, bias, fmt_id, N, K, g, had, out_id=-1):
     lib = _lib.load()
     Bt = x2.shape[0]
     y = torch.empty((Bt, N), dtype=_OUT[out_id] or x2.dtype, device=x2.device)
     if tc_eligible(fmt_id, K, g, Bt):
         return _linear_rows_tc(x2, qweight, scales, bias, N, K, had, y)
-    with torch.cuda.device(x2.device):
+    xd, yd = _DT[x2.dtype], _DT[y.dtype]
+    qw_p, sc_p, cb_p, bias_p = _ptr(qweight), _ptr(scales), _ptr(codebook), _ptr(bias)
+    with _on(x2.device):
+        stream = _stream()
         for b0 in range(0, Bt, MAX_GEMV_BATCH):
             b1 = min(Bt, b0 + MAX_GEMV_BATCH)
-            xs, ys = x2[b0:b1], y[b0:b1]
+            xs, ys = (x2, y) if Bt <= MAX_GEMV_BATCH else (x2[b0:b1], y[b0:b1])
             # split-K scratch (fp32 partial outputs) when the staged batch would not fit in shared memory
-            wsb = lib.jq_workspace_bytes(0, N, K, b1 - b0)
+            key = (N, K, b1 - b0)
+            wsb = _wsb_cache.get(key)
+            if wsb is None:
+                wsb = _wsb_cache[key] = lib.jq_workspace_bytes(0, N, K, b1 - b0)
             ws = _workspace(x2.device, wsb)[:wsb] if wsb else None
 
             def call(ws_t):
                 nb = ws_t.numel() if ws_t is not None else 0
                 if fmt_id == _lib.JQ_FMT_E2M1:
-                    return lib.jq_gemv_e2m1(_ptr(qweight), _ptr(scales), _ptr(xs), _ptr(bias), _ptr(ys), N, K,
-                                            b1 - b0, g, had, _DT[x2.dtype], _DT[y.dtype], _ptr(ws_t), nb, _stream())
-                return lib.jq_gemv_gf4(_ptr(qweight), _ptr(scales), _ptr(codebook), _ptr(xs), _ptr(bias), _ptr(ys),
-                                       N, K, b1 - b0, g, had, _DT[x2.dtype], _DT[y.dtype], _ptr(ws_t), nb, _stream())
+                    return lib.jq_gemv_e2m1(qw_p, sc_p, _ptr(xs), bias_p, _ptr(ys), N, K,
+                                            b1 - b0, g, had, xd, yd, _ptr(ws_t), nb, stream)
+                return lib.jq_gemv_gf4(qw_p, sc_p, cb_p, _ptr(xs), bias_p, _ptr(ys),
+                                       N, K, b1 - b0, g, had, xd, yd, _ptr(ws_t), nb, stream)
 
             st = call(ws)
             if st == -6 and ws is not None:   # workspace too small for this group size: sub-batch path
                 st = call(None)
-            _lib.check(st, "jq_gemv")
+            if st:
+                _lib.check(st, "jq_gemv")
     return y
 
 
