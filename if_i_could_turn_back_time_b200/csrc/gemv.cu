@@ -1,13 +1,19 @@
-// Fused 4-bit dequantise + GEMV for B200 (sm_100a), batch 1..8, CUDA cores.
+// Fused 4-bit dequantise + GEMV for B200 (sm_100a), batch 1..8.
 //
-// Data path: packed weight rows stream from HBM with 128-bit no-allocate
-// loads (each byte is read exactly once); the activation is rotated (block
-// Hadamard), normalised by a power of two and rounded to fp16 once per CTA
-// into shared memory; E2M1 nibbles are converted two at a time by the sm_100a
-// cvt.rn.f16x2.e2m1x2 instruction, GF4 nibbles index a per-row 16-entry fp16
-// table in shared memory; products fp16 x fp16 are exact in fp32 and are
-// accumulated with the mixed-precision fma.rn.f32.f16; group scales are
-// applied in fp32 per 32-code chunk; rows are reduced with warp shuffles.
+// Data path: packed weight rows stream from HBM exactly once (cp.async into
+// per-thread or per-warp shared-memory rings, or straight into registers); the
+// activation is rotated (block Hadamard), normalised by a power of two and
+// rounded to fp16 once per CTA into shared memory; E2M1 nibbles are converted
+// two at a time by the sm_100a cvt.rn.f16x2.e2m1x2 instruction, GF4 nibbles
+// index per-row 16-entry fp16 tables in shared memory; products fp16 x fp16
+// are exact in fp32 and accumulated in fp32; group scales are applied in fp32.
+// Row loops (run_rows picks one per problem):
+//   cta_rows            batch 1 (and any shape the others do not take): one FMA
+//                       per code (fma.rn.f32.f16), warp = T rows x all of K
+//   cta_rows_gf4_direct GF4 batch 1: the same with rows loaded to registers
+//   cta_rows_mma        E2M1 batch 2..8: dot products on mma.sync.m16n8k16
+//   cta_rows_mma_gf4    GF4 batch 3..8: per-lane table columns + the same MMA
+//   rows_k_tiled        grouped launches whose batch x K exceeds shared memory
 #include "common.cuh"
 
 namespace jq {
