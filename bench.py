@@ -15,10 +15,13 @@ shape is quantised with the real packer and copied into distinct allocations
 for every use, so a token reads 3.39 GB of distinct HBM (far beyond L2).
 
 N > 1 (torchrun, one rank per GPU): every matrix is row-sharded over the
-ranks and the output slices are exchanged by one NCCL all-gather per step.
+ranks; the output slices reach every rank either by peer stores from the GEMV
+epilogue plus a barrier (--exchange fused, the default) or by one NCCL
+all-gather per step (--exchange nccl).
 
-The line printed by rank 0 follows the driver's contract; see --help of each
-field in DESIGN.md.
+Rank 0 prints one JSON line: metric, value, unit, per-step time, clocks seen
+during the timed region, the end-to-end figure with host copies (e2e), the
+roofline of the dominant kernel, and (N = 1) a CPU baseline.
 """
 from __future__ import annotations
 

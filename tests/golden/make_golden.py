@@ -1,7 +1,7 @@
 """Generate the committed golden vectors under tests/golden/.
 
-Run once in a container that has the reference checkout:
-    python tests/golden/make_golden.py /root/reference
+Run once on a machine that has the reference checkout:
+    python tests/golden/make_golden.py <path to the reference checkout>
 The reference has no packed format, so the *format* side of every vector
 comes from the CPU oracle (oracle/formats.py, oracle/jenks.py).  The
 *operator* side is the reference's own code: its ``QuantLinear`` class
@@ -132,4 +132,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path to the reference checkout>")
+    main(sys.argv[1])
