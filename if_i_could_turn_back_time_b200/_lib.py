@@ -46,6 +46,13 @@ _SIGNATURES = {
                                 c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "jq_gemm_e2m1_tc_multi": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "jq_tc_status": (c_int, [c_void_p, c_void_p]),
+    "jq_ta_workspace_bytes": (c_size_t, [c_void_p, c_int, c_int]),
+    "jq_ta_plan_bytes": (c_size_t, [c_int]),
+    "jq_ta_plan": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p, c_size_t]),
+    "jq_gemm_ta_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "jq_gemm_ta": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                           c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "jq_ta_status": (c_int, [c_void_p, c_int, c_void_p]),
     "jq_selftest_bounded_wait": (c_int, [c_void_p, ctypes.c_uint, c_void_p]),
     "jq_grouped_plan_bytes": (c_size_t, [c_int]),
     "jq_grouped_plan": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_size_t]),

@@ -1,0 +1,1221 @@
+// Packed 4-bit weights x activations on the 5th-generation tensor cores with
+// the decoded weights handed over in tensor memory (tcgen05, sm_100a).
+//
+// One persistent CTA per SM works through 128-row tiles of the weight matrices.
+// A decode thread owns one weight row of the tile (= one tensor-memory lane)
+// and one half of the 256-code steps of that row:
+//   * the packed codes of a warp's 32 rows arrive by TMA (cp.async.bulk.tensor,
+//     one 32-row x 128-byte box per step with the 128-byte swizzle, completion
+//     counted on an mbarrier), so that every lane reads its own row without
+//     bank conflicts; later steps are prefetched into L2 by the same engine;
+//   * GF4: a byte (two codes) indexes the row's 256-entry table of fp16 pairs,
+//     built once per tile in a shared-memory column that only this lane's bank
+//     serves (one conflict-free 32-bit lookup per two codes, the address formed
+//     by one dp4a); E2M1: cvt.rn.f16x2.e2m1x2 per byte, times the group's fp16
+//     scale in fp16x2;
+//   * the fp16 values go to tensor memory with tcgen05.st as the A operand
+//     (M = 128 rows, K = 16 per instruction) of tcgen05.mma kind::f16; the B
+//     operand is the prepared activation (rotated, normalised by a power of
+//     two, fp16, in the K-major core-matrix layout) that a producer thread
+//     streams from global memory, one 128-code chunk per bulk copy;
+//   * GF4 keeps one fp32 accumulator per 128-code scale group in tensor memory;
+//     the thread reads its row's sums back with tcgen05.ld and applies the
+//     group's fp16 scale in fp32, so every product and every scale stays exact
+//     (the results differ from the FMA kernels only in summation order).
+//     E2M1 folds the scale into the fp16 weight (one rounding per weight) and
+//     accumulates the whole row in one accumulator.
+// The multiply-accumulate work thus costs the CUDA cores nothing, whatever the
+// batch (up to 64 columns per pass), and the lookups are halved.
+//
+// Every wait on an mbarrier is bounded: on expiry the CTA raises a status word
+// in the workspace, all roles leave their loops, tensor memory is freed and
+// the kernel returns.  Nothing traps or spins without a limit.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <string.h>
+#include <stdlib.h>
+
+namespace jqta {
+
+constexpr int kDecodeWarps = 8;              // warps 0-3: first half of the steps, warps 4-7: second half
+constexpr int kThreads = (kDecodeWarps + 2) * 32;   // + MMA issuer warp + activation producer warp
+constexpr int kTileM = 128;
+constexpr int kSW = 2;                       // stages of a decode warp's weight ring
+constexpr int kWStage = 32 * 128;            // bytes of a weight stage: 32 rows x 128 bytes (256 codes), swizzled by TMA
+constexpr int kXRingBytes = 24 * 1024;         // activation ring: stages of max(2 KB, one 128-code chunk)
+constexpr int kXMaxStages = 12;
+#ifndef JQ_L2AHEAD
+#define JQ_L2AHEAD 6
+#endif
+constexpr int kL2Ahead = JQ_L2AHEAD;                  // steps by which the L2 prefetch runs ahead of the shared-memory fills
+constexpr int kTabBytes = 4 * 256 * 128;     // GF4: 256 entries x 32 lanes x 4 bytes per 32-row quarter
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kHeaderBytes = 1024;           // workspace: int status
+
+struct TaProblem {
+    const uint8_t *qw;
+    const __half *scales;
+    const __half *codebook;
+    const void *x;          // activations [B, K] as the caller gave them
+    const float *bias;
+    void *y;
+    __half *xprep;          // prepared activation: [K / 8][B rows][8 halves]
+    float *xscale;          // [B] 2^e of each batch row (the power of two taken out before rounding to fp16)
+    int N, K, g, had;
+    int ldw;                // bytes between packed rows
+    int lds;                // scales between rows
+    int ldy;                // outputs between batch rows
+    int tile0;              // first tile of this problem in the launch's tile sequence
+};
+
+struct PeerInfo {
+    int n;
+    long long delta[8];
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("{ .reg .b64 t; mbarrier.arrive.shared::cta.b64 t, [%0]; }" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("{ .reg .b64 t; mbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1; }" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false (and the CTA-wide error flag raised) when it gives up, after kSpinLimit polls or
+// about 0.25 s of SM clock, whichever comes first; also false as soon as another thread has raised the flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *err) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if (*err) return false;
+        if (i > 8192) {
+            __nanosleep(64);
+            if (clock64() - t0 > 500000000LL) break;
+        }
+    }
+    *err = JQ_ERR_TIMEOUT;
+    return false;
+}
+// global -> shared bulk copy (16-byte aligned, a multiple of 16 bytes); its bytes are counted on the mbarrier
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// 2-D tiled TMA load: box at (x bytes, y rows) of the tensor map -> shared memory; x must be a multiple of 16
+__device__ __forceinline__ void tma_2d_g2s(uint32_t dst, const void *tmap, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_2d_prefetch_l2(const void *tmap, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// K-major operand in shared memory without swizzle: 8 rows x 16 bytes are contiguous; lbo = bytes between
+// the two 16-byte K chunks of one MMA, sbo = bytes between 8-row groups (bits 46-47 = 1: sm_100 descriptor).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fffu);
+    d |= (uint64_t)((lbo >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+// kind::f16 instruction descriptor: D = fp32, A = B = fp16, both K-major
+__host__ __device__ constexpr uint32_t idesc_f16(int M, int N) {
+    return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// D[128 x N] (+)= A[128 x 16] (tensor memory) . B[N x 16]^T (shared memory)
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+                 "  tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t dp4a_u(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// e with amax * 2^-e below 2^15 after the rotation's worst-case growth (the rule of the GEMV kernels)
+__device__ __forceinline__ int act_exponent(float amax, bool had) {
+    uint32_t bits = __float_as_uint(amax);
+    int field = (bits >> 23) & 0xff;
+    if (field == 0xff || (bits & 0x7fffffffu) == 0) return 0;
+    int e = field - 127 - (had ? 10 : 14);
+    return max(-100, min(100, e));
+}
+
+// ---- activation preparation -----------------------------------------------------
+// One block per (problem, batch row): x -> (x 2^-e) -> block Hadamard -> fp16, written as
+// [8-code piece][batch row][8 halves].  Copied to shared memory as it is, this is the K-major operand
+// layout of the MMA with a piece stride of 16 B bytes: row n of piece c sits at (c B + n) 16 bytes.  The MMA
+// always reads 16 rows; rows >= B are whatever follows (the next pieces), and their accumulator columns
+// are never read.
+__global__ void __launch_bounds__(256) ta_prepare_kernel(const TaProblem *probs, TaProblem single, int B,
+                                                          int x_dtype) {
+    __shared__ float sred[8];
+    __shared__ int sexp;
+    const int pi = blockIdx.x / B, b = blockIdx.x % B;
+    const TaProblem p = probs ? probs[pi] : single;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float m = 0.f;
+    for (int k = tid; k < p.K; k += 256) m = fmaxf(m, fabsf(jq::load_act(p.x, (size_t)b * p.K + k, x_dtype)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) sred[warp] = m;
+    __syncthreads();
+    if (tid == 0) {
+        float mm = 0.f;
+        for (int w = 0; w < 8; ++w) mm = fmaxf(mm, sred[w]);
+        sexp = act_exponent(mm, p.had != 0);
+        p.xscale[b] = __uint_as_float((uint32_t)(127 + sexp) << 23);
+    }
+    __syncthreads();
+    const float down = __uint_as_float((uint32_t)(127 - sexp) << 23);
+    for (int blk = warp; blk * 128 < p.K; blk += 8) {
+        float v[4];
+        const int k0 = blk * 128 + lane * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = jq::load_act(p.x, (size_t)b * p.K + k0 + j, x_dtype) * down;
+        if (p.had) jq::fwht128_warp(v, lane);
+        __half2 h01 = __floats2half2_rn(v[0], v[1]), h23 = __floats2half2_rn(v[2], v[3]);
+        const size_t off = (((size_t)blk * 16 + (lane >> 1)) * B + b) * 8 + (lane & 1) * 4;
+        *reinterpret_cast<uint2 *>(p.xprep + off) =
+            make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
+    }
+}
+
+// ---- main kernel --------------------------------------------------------------------
+// tensor-memory columns: kRing regions per half (half h, slot s) of kRegion columns: A slices at +0 (64 columns
+// = one 128-code group), the group's accumulator at +64; then NB columns through which the second half's
+// threads hand their partial sums to the first half's at the end of a tile.
+constexpr int kRing = 3;                     // groups a half may have in flight (stored, not yet folded)
+template <int NB>
+struct Cols {
+    static constexpr int kRegion = 64 + NB;
+    static constexpr int kExchange = 2 * kRing * kRegion;
+    static_assert(kExchange + NB <= 512, "tensor memory");
+};
+
+struct Smem {
+    static constexpr int kTab = 0;
+    static constexpr int kWRing = kTab + kTabBytes;
+    static constexpr int kXRing = kWRing + kDecodeWarps * kSW * kWStage;
+    static constexpr int kBars = kXRing + kXRingBytes + 512;    // + what the MMA reads past the last chunk (rows >= B)
+    static constexpr int kNumBars = kDecodeWarps * kSW + 4 * kRing + 2 * kXMaxStages + 4;   // weights, A full, D full, x full/empty, quarter sync
+    static constexpr int kBytes = kBars + kNumBars * 8 + 1024;  // + slack for the 1 KB alignment of the base (TMA swizzle)
+};
+
+// geometry of the activation ring for a batch of B rows: a chunk (128 codes) is 256 B bytes; a stage holds
+// as many whole chunks as fit in 2 KB (at least one)
+struct XGeom {
+    int chunk, gps, stage, nstages;
+    __host__ __device__ explicit XGeom(int B) {
+        chunk = 256 * B;
+        gps = 2048 / chunk > 0 ? 2048 / chunk : 1;
+        stage = gps * chunk;
+        nstages = kXRingBytes / stage < kXMaxStages ? kXRingBytes / stage : kXMaxStages;
+    }
+};
+
+// A thread's walk over its (tile, step) pairs: used three times per decode thread (L2 prefetch, shared-memory
+// fill, consumption), each a fixed distance behind the previous one.
+struct StepCursor {
+    int tile, pi, j, n;
+    int x, y;               // byte offset in the packed row, first row of the warp's 32
+    const void *map;
+};
+
+template <int NB>
+__global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProblem *probs, const CUtensorMap *maps,
+                                                                   const __grid_constant__ TaProblem single,
+                                                                   const __grid_constant__ CUtensorMap single_map, int nprob,
+                                                                   const int *tile_start, const int *cta_first,
+                                                                   int B, int y_dtype, PeerInfo peers, int *status) {
+    using C = Cols<NB>;
+    using S = Smem;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_err;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = sbase + S::kBars;
+    auto wbar = [&](int w, int s) { return bars + 8u * (w * kSW + s); };
+    auto abar = [&](int h, int s) { return bars + 8u * (kDecodeWarps * kSW + h * kRing + s); };
+    auto dbar = [&](int h, int s) { return bars + 8u * (kDecodeWarps * kSW + 2 * kRing + h * kRing + s); };
+    auto xbar = [&](int s) { return bars + 8u * (kDecodeWarps * kSW + 4 * kRing + s); };
+    auto xebar = [&](int s) { return bars + 8u * (kDecodeWarps * kSW + 4 * kRing + kXMaxStages + s); };
+    auto qbar = [&](int q) { return bars + 8u * (kDecodeWarps * kSW + 4 * kRing + 2 * kXMaxStages + q); };
+    volatile int *err = &s_err;
+    const XGeom xg(B);
+
+    if (tid == 0) {
+        s_err = 0;
+        for (int w = 0; w < kDecodeWarps; ++w)
+            for (int s = 0; s < kSW; ++s) mbar_init(wbar(w, s), 1);     // one arrive.expect_tx per fill
+        for (int h = 0; h < 2; ++h)
+            for (int s = 0; s < kRing; ++s) {
+                mbar_init(abar(h, s), 128);                             // the 128 decode threads of the half
+                mbar_init(dbar(h, s), 1);                               // one tcgen05.commit
+            }
+        for (int s = 0; s < kXMaxStages; ++s) { mbar_init(xbar(s), 1); mbar_init(xebar(s), 1); }
+        for (int q = 0; q < 4; ++q) mbar_init(qbar(q), 64);             // the two warps that share a table quarter
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kDecodeWarps) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+
+    // this CTA's tiles
+    int tile_lo, tile_hi;
+    if (nprob == 0) {   // one problem, passed by value: an even split of its tiles
+        const int nt = (single.N + kTileM - 1) / kTileM;
+        tile_lo = (int)((long long)nt * blockIdx.x / gridDim.x);
+        tile_hi = (int)((long long)nt * (blockIdx.x + 1) / gridDim.x);
+    } else {
+        tile_lo = cta_first[blockIdx.x];
+        tile_hi = cta_first[blockIdx.x + 1];
+    }
+    auto problem_of = [&](int &pi, int tile) -> TaProblem {
+        if (nprob == 0) return single;
+        while (pi + 1 < nprob && tile_start[pi + 1] <= tile) ++pi;
+        return probs[pi];
+    };
+
+    if (warp < kDecodeWarps) {
+        // =============================== decode threads ===============================
+#ifdef JQ_TA_PROF
+        long long pt[6] = {0, 0, 0, 0, 0, 0};
+        const long long pt_start = clock64();
+#define PT(i, expr) { const long long _t = clock64(); expr; pt[i] += clock64() - _t; }
+#else
+#define PT(i, expr) expr;
+#endif
+        const int q = warp & 3, h = warp >> 2;
+        const int r = q * 32 + lane;                       // row of the tile = tensor-memory lane
+        const uint32_t lane_t = tmem + ((uint32_t)(q * 32) << 16);
+        const uint32_t tcol = sbase + S::kTab + q * (256 * 128) + lane * 4;   // entry e of this row at tcol + 128 e
+        const uint32_t wring = sbase + S::kWRing + warp * (kSW * kWStage);     // + stage * kWStage; 1 KB aligned
+        // 16-byte piece c of this lane's row sits at piece c ^ (lane & 7) of the row (128-byte swizzle)
+        const uint32_t lrow = lane * 128, lkey = (lane & 7) << 4;
+
+        // position a cursor on step 0 of its tile (skipping tiles in which this half has no step)
+        auto open = [&](StepCursor &c) {
+            while (c.tile < tile_hi) {
+                const TaProblem p = problem_of(c.pi, c.tile);
+                c.n = ((p.K >> 8) - h + 1) >> 1;
+                c.x = h * 128;
+                c.y = (c.tile - p.tile0) * kTileM + q * 32;     // rows past N read as zeros
+                c.map = nprob ? &maps[c.pi] : &single_map;
+                c.j = 0;
+                if (c.n > 0) return;
+                ++c.tile;
+            }
+        };
+        auto advance = [&](StepCursor &c) {
+            c.x += 256;
+            if (++c.j == c.n) { ++c.tile; open(c); }
+        };
+        StepCursor pf{tile_lo, 0, 0, 0, 0, 0, nullptr}, is{tile_lo, 0, 0, 0, 0, 0, nullptr};
+        int i_stage = 0;
+        auto prefetch = [&]() {     // the box of a later step, into L2
+            if (pf.tile < tile_hi) {
+                if (lane == 0) tma_2d_prefetch_l2(pf.map, pf.x, pf.y);
+                advance(pf);
+            }
+        };
+        auto issue = [&]() {
+            if (is.tile < tile_hi) {
+                if (lane == 0) {
+                    const uint32_t bar = wbar(warp, i_stage);
+                    mbar_expect_tx(bar, kWStage);
+                    tma_2d_g2s(wring + i_stage * kWStage, is.map, is.x, is.y, bar);
+                }
+                advance(is);
+            }
+            i_stage = (i_stage + 1 == kSW) ? 0 : i_stage + 1;
+            prefetch();
+        };
+        open(pf);
+        open(is);
+        for (int s = 0; s < kSW + kL2Ahead; ++s) prefetch();
+#pragma unroll
+        for (int s = 0; s < kSW; ++s) issue();
+
+        // ---- consumer state
+        uint32_t wcount = 0;        // weight stages consumed so far
+        uint32_t t_h = 0;           // groups this half has handed to the MMA so far
+        uint32_t qcount = 0;        // quarter syncs so far
+        uint32_t t_fold = 0;        // groups folded into acc so far (t_fold <= t_h)
+        unsigned short raw_q[kRing] = {};   // fp16 scales (bits) of the groups in flight, by slot
+        float xsc[NB];              // 2^e of the batch rows (first half's threads, which write the outputs)
+        float acc[NB];
+        bool have_prev = false;     // a finished tile waiting for its last group and its output
+        TaProblem prev_p = single;
+        int prev_row = 0;
+
+        int c_pi = 0;
+        uint4 cb0 = make_uint4(0, 0, 0, 0), cb1 = cb0;     // this row's codebook (next tile's, once the tables are built)
+        auto fetch_codebook = [&](int tile) {
+            if (tile < tile_hi) {
+                int pi2 = c_pi;
+                const TaProblem p = problem_of(pi2, tile);
+                const int row = min((tile - p.tile0) * kTileM + r, p.N - 1);
+                const uint4 *src = reinterpret_cast<const uint4 *>(p.codebook + (size_t)row * 16);
+                cb0 = __ldg(src);
+                cb1 = __ldg(src + 1);
+            }
+        };
+        auto quarter_sync = [&]() -> bool {
+            mbar_arrive(qbar(q));
+            const bool ok = mbar_wait(qbar(q), qcount & 1, err);
+            ++qcount;
+            return ok;
+        };
+        // fold the accumulator of group pend_t (scaled) into acc
+        auto fold_one = [&]() -> bool {   // the oldest group in flight
+            const uint32_t s = t_fold % kRing;
+            bool ok;
+            PT(2, ok = __all_sync(0xffffffffu, mbar_wait(dbar(h, s), (t_fold / kRing) & 1, err)))
+            if (!ok) return false;
+            tc_fence_after();
+            unsigned short raw = raw_q[0];
+#pragma unroll
+            for (int i = 1; i < kRing; ++i) raw = (s == (uint32_t)i) ? raw_q[i] : raw;
+            const float pend_scale = __half2float(__ushort_as_half(raw));
+#pragma unroll
+            for (int c = 0; c < NB; c += 16) {
+                uint32_t d[16];
+                tmem_ld16(lane_t + (h * kRing + s) * C::kRegion + 64 + c, d);
+                PT(3, tmem_wait_ld())
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[c + i] = fmaf(__uint_as_float(d[i]), pend_scale, acc[c + i]);
+            }
+            ++t_fold;
+            return true;
+        };
+        // outputs of the finished tile: the second half hands its sums over through tensor memory
+        auto finish_prev = [&]() -> bool {
+            if (!have_prev) return true;
+            while (t_fold < t_h)
+                if (!fold_one()) return false;
+            if (h == 1) {
+#pragma unroll
+                for (int c = 0; c < NB; c += 16) {
+                    uint32_t v[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(acc[c + i]);
+                    tmem_st16(lane_t + C::kExchange + c, v);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+            }
+            if (!quarter_sync()) return false;
+            if (h == 0) {
+                tc_fence_after();
+                const bool live = prev_row < prev_p.N;
+                const float bias = (live && prev_p.bias) ? prev_p.bias[prev_row] : 0.f;
+#pragma unroll
+                for (int c = 0; c < NB; c += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(lane_t + C::kExchange + c, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int b = c + i;
+                        if (live && b < B) {
+                            const float o = fmaf(acc[b] + __uint_as_float(v[i]), xsc[b], bias);
+                            for (int cpy = 0; cpy < peers.n; ++cpy)
+                                jq::store_out(reinterpret_cast<char *>(prev_p.y) + peers.delta[cpy],
+                                              (size_t)b * prev_p.ldy + prev_row, o, y_dtype);
+                        }
+                    }
+                }
+                tc_fence_before();
+            }
+            have_prev = false;
+            return true;
+        };
+        // 32 codes (four words) -> 16 fp16 pairs
+        auto lookup16 = [&](const uint4 &w4, uint32_t (&v)[16]) {
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                const uint32_t w = wi == 0 ? w4.x : (wi == 1 ? w4.y : (wi == 2 ? w4.z : w4.w));
+#pragma unroll
+                for (int bj = 0; bj < 4; ++bj) v[wi * 4 + bj] = lds32(dp4a_u(w, 0x80u << (8 * bj), tcol));
+            }
+        };
+
+        fetch_codebook(tile_lo);
+        bool ok = true;
+        for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
+            const TaProblem p = problem_of(c_pi, tile);
+            const int row_raw = (tile - p.tile0) * kTileM + r;
+            const int row = min(row_raw, p.N - 1);
+            // ---- the pair table of this row (this thread fills the entries whose second code is in its half)
+            const long long _tb = clock64();
+            if (!(ok = quarter_sync())) break;          // both warps are done with the previous tile's lookups
+            {
+                const uint32_t c[8] = {cb0.x, cb0.y, cb0.z, cb0.w, cb1.x, cb1.y, cb1.z, cb1.w};
+                uint32_t ch[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) ch[i] = h ? c[4 + i] : c[i];
+                const uint32_t tb = tcol + h * (128 * 128);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+#pragma unroll
+                    for (int lo = 0; lo < 16; ++lo) {
+                        const uint32_t e = __byte_perm(c[lo >> 1], ch[i >> 1],
+                                                       ((lo & 1) ? 0x32u : 0x10u) | (((i & 1) ? 0x76u : 0x54u) << 8));
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(tb + (i * 16 + lo) * 128), "r"(e) : "memory");
+                    }
+            }
+            fetch_codebook(tile + 1);
+            // the previous tile's last group has had the table build to finish
+            const bool had_prev = have_prev;
+            if (!(ok = finish_prev())) break;           // (its quarter sync also publishes the new table)
+            if (!had_prev) { if (!(ok = quarter_sync())) break; }
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                acc[b] = 0.f;
+                if (h == 0) xsc[b] = b < B ? p.xscale[b] : 0.f;   // in flight during the tile, needed at its end
+            }
+#ifdef JQ_TA_PROF
+            pt[4] += clock64() - _tb;
+#endif
+
+            const int nsteps = ((p.K >> 8) - h + 1) >> 1;
+            const unsigned short *srow = reinterpret_cast<const unsigned short *>(p.scales) + (size_t)row * p.lds;
+            const int gshift = 31 - __clz(p.g >> 7);   // log2 of the 128-code groups per scale (a power of two)
+            for (int j = 0; j < nsteps && ok; ++j) {
+                const int stage = wcount % kSW;
+                PT(0, ok = __all_sync(0xffffffffu, mbar_wait(wbar(warp, stage), (wcount / kSW) & 1, err)))
+                if (!ok) break;
+                ++wcount;
+                const uint32_t slot = wring + stage * kWStage + lrow;
+                const int sg = 2 * j + h;
+#pragma unroll
+                for (int gi = 0; gi < 2; ++gi) {
+                    const int grp = 2 * sg + gi;
+                    const unsigned short scale_raw = __ldg(srow + (grp >> gshift));
+                    // slot t % kRing is free once group t - kRing has been folded
+                    if (t_h - t_fold == kRing && !(ok = fold_one())) break;
+                    const uint32_t t = t_h, s = t % kRing;
+                    const uint32_t a_t = lane_t + (h * kRing + s) * C::kRegion;
+                    // the lookups of the next 32 codes are issued before the previous 16 pairs are stored
+                    uint4 w4[4];
+#pragma unroll
+                    for (int part = 0; part < 4; ++part) w4[part] = lds128(slot + (((gi * 4 + part) << 4) ^ lkey));
+                    uint32_t va[16], vb[16];
+                    lookup16(w4[0], va);
+                    lookup16(w4[1], vb);
+                    tmem_st16(a_t, va);
+                    lookup16(w4[2], va);
+                    tmem_st16(a_t + 16, vb);
+                    lookup16(w4[3], vb);
+                    tmem_st16(a_t + 32, va);
+                    tmem_st16(a_t + 48, vb);
+                    PT(1, tmem_wait_st())
+                    tc_fence_before();
+                    mbar_arrive(abar(h, s));
+                    ++t_h;
+#pragma unroll
+                    for (int i = 0; i < kRing; ++i) raw_q[i] = (s == (uint32_t)i) ? scale_raw : raw_q[i];
+                }
+                if (!ok) break;
+                __syncwarp();                           // every lane has read its row of the stage
+                fence_async_smem();
+                issue();                                // refill the stage just read
+            }
+            have_prev = true;
+            prev_p = p;
+            prev_row = row_raw;
+        }
+        if (ok) ok = finish_prev();
+#ifdef JQ_TA_PROF
+        pt[5] = clock64() - pt_start;
+        if (blockIdx.x == 0 && lane == 0)
+            for (int i = 0; i < 6; ++i) reinterpret_cast<long long *>(status)[8 + warp * 6 + i] = pt[i];
+#endif
+    } else if (warp == kDecodeWarps) {
+        // =============================== MMA issuer ===============================
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_f16(kTileM, NB);
+            uint32_t tslot[2] = {0, 0}, tpar[2] = {0, 0};   // per half: slot of its next group, parity of that slot's phase
+            uint32_t xs = 0, xpar = 0;                      // activation stage in use and its phase parity
+            int pi = 0;
+            bool ok = true;
+            const uint32_t lbo = (uint32_t)B * 16;
+#ifdef JQ_TA_PROF
+            long long mt[4] = {0, 0, 0, 0};
+            const long long mt0 = clock64();
+#define MT(i, expr) { const long long _t = clock64(); expr; mt[i] += clock64() - _t; }
+#else
+#define MT(i, expr) expr;
+#endif
+            for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
+                const TaProblem p = problem_of(pi, tile);
+                const int ng = p.K >> 7;
+                int gin = 0;
+                uint32_t xb = sbase + S::kXRing + xs * xg.stage;
+                for (int g = 0; g < ng; ++g) {
+                    const int h = (g >> 1) & 1;
+                    const uint32_t s = tslot[h];
+                    if (gin == 0) { MT(0, ok = mbar_wait(xbar(xs), xpar, err)) if (!ok) break; }
+                    MT(1, ok = mbar_wait(abar(h, s), tpar[h], err))
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_t = tmem + (h * kRing + s) * C::kRegion, d_t = a_t + 64;
+                    MT(2,
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        mma_f16_ts(d_t, a_t + 8 * i, smem_desc(xb + 2 * i * lbo, lbo, 128), idesc, i > 0);
+                    )
+                    MT(3, mma_commit(dbar(h, s)))
+                    if (s + 1 == kRing) { tslot[h] = 0; tpar[h] ^= 1; } else tslot[h] = s + 1;
+                    xb += xg.chunk;
+                    if (++gin == xg.gps || g == ng - 1) {
+                        mma_commit(xebar(xs));          // the stage's chunks have been multiplied
+                        gin = 0;
+                        if (++xs == (uint32_t)xg.nstages) { xs = 0; xpar ^= 1; }
+                        xb = sbase + S::kXRing + xs * xg.stage;
+                    }
+                }
+            }
+#ifdef JQ_TA_PROF
+            if (blockIdx.x == 0) {
+                for (int i = 0; i < 4; ++i) reinterpret_cast<long long *>(status)[8 + 48 + i] = mt[i];
+                reinterpret_cast<long long *>(status)[8 + 52] = clock64() - mt0;
+            }
+#endif
+        }
+    } else {
+        // =============================== activation producer ===============================
+        if (lane == 0) {
+            uint32_t xc = 0;
+            int pi = 0;
+            bool ok = true;
+            for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
+                const TaProblem p = problem_of(pi, tile);
+                const int ng = p.K >> 7;
+                for (int g0 = 0; g0 < ng; g0 += xg.gps, ++xc) {
+                    const int g1 = min(ng, g0 + xg.gps);
+                    const int xs = xc % xg.nstages;
+                    const uint32_t round = xc / xg.nstages;
+                    if (round > 0 && !(ok = mbar_wait(xebar(xs), (round - 1) & 1, err))) break;
+                    const uint32_t bytes = (uint32_t)(g1 - g0) * xg.chunk;
+                    mbar_expect_tx(xbar(xs), bytes);
+                    bulk_g2s(sbase + S::kXRing + xs * xg.stage,
+                             reinterpret_cast<const unsigned char *>(p.xprep) + (size_t)g0 * xg.chunk, bytes, xbar(xs));
+                }
+            }
+        }
+    }
+
+    // ---- teardown
+    if (*err) {   // a wait gave up: let the copies still in flight land before the CTA's shared memory goes away
+        for (int i = 0; i < 400; ++i) __nanosleep(256);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && s_err) atomicExch(status, s_err);
+    if (warp == kDecodeWarps) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+
+// ---- GF4, batch 1..2 on the CUDA cores ------------------------------------------------
+// Same tiles, same TMA weight ring, same per-row pair tables as the tensor-memory kernel above, but the
+// multiply-accumulate stays in the decode threads: lane = weight row, so all lanes of a warp need the same
+// activation values, which they read as broadcast 16-byte shared-memory loads (one wavefront per eight
+// codes) from the prepared activation of the whole problem, and a looked-up pair feeds two
+// fma.rn.f32.f16 (fp16 x fp16 exact, fp32 accumulation).  Per 128-code group the partial sum is scaled by
+// the group's fp16 scale in fp32.  At batch 1 this costs about 2.2 instructions and 0.75 shared-memory
+// wavefronts per code, where one 16-bit lookup per code costs 1.2 wavefronts; the tensor pipe, whose
+// K = 16 instructions have a floor of about 45 clocks whatever the batch, is not involved.
+constexpr int kLutSplit = 4;                         // warps that share a 32-row quarter, each taking every 4th group
+constexpr int kLutWarps = 4 * kLutSplit;
+constexpr int kLutThreads = kLutWarps * 32;
+constexpr int kLutStage = 32 * 64;                   // a weight stage: 32 rows x 64 bytes (one 128-code group), 64-byte swizzle
+struct LutSmem {
+    static constexpr int kTab = 0;
+    static constexpr int kWRing = kTab + kTabBytes;
+    static constexpr int kX = kWRing + kLutWarps * kSW * kLutStage;      // prepared activation of the current problem
+    static constexpr int kXBytes = 28 * 1024;
+    static constexpr int kPart = kX + kXBytes;                           // partial sums of the other warps of a quarter
+    static constexpr int kBars = kPart + (kLutSplit - 1) * 128 * 2 * 4;
+    static constexpr int kNumBars = kLutWarps * kSW + 4 + 2;             // weights, quarter sync, x free / x full
+    static constexpr int kBytes = kBars + kNumBars * 8 + 1024;
+};
+
+// acc0 += lo(w) * lo(x), acc1 += hi(w) * hi(x): fp16 operands, exact products, fp32 accumulation
+__device__ __forceinline__ void fma_pair(float &acc0, float &acc1, uint32_t w, uint32_t x) {
+    asm("{ .reg .b16 wl, wh, xl, xh; mov.b32 {wl, wh}, %2; mov.b32 {xl, xh}, %3;\n"
+        "  fma.rn.f32.f16 %0, wl, xl, %0; fma.rn.f32.f16 %1, wh, xh, %1; }"
+        : "+f"(acc0), "+f"(acc1) : "r"(w), "r"(x));
+}
+
+template <int B>
+__global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProblem *probs, const CUtensorMap *maps,
+                                                                  const __grid_constant__ TaProblem single,
+                                                                  const __grid_constant__ CUtensorMap single_map,
+                                                                  int nprob, const int *tile_start, const int *cta_first,
+                                                                  int y_dtype, PeerInfo peers, int *status) {
+    using S = LutSmem;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ int s_err;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char *sgen = smem_raw + (sbase - smem_u32(smem_raw));
+    const uint32_t bars = sbase + S::kBars;
+    auto wbar = [&](int w, int s) { return bars + 8u * (w * kSW + s); };
+    auto qbar = [&](int q) { return bars + 8u * (kLutWarps * kSW + q); };
+    const uint32_t xfree = bars + 8u * (kLutWarps * kSW + 4), xfull = xfree + 8;
+    volatile int *err = &s_err;
+    if (tid == 0) {
+        s_err = 0;
+        for (int w = 0; w < kLutWarps; ++w)
+            for (int s = 0; s < kSW; ++s) mbar_init(wbar(w, s), 1);
+        for (int q = 0; q < 4; ++q) mbar_init(qbar(q), 32 * kLutSplit);
+        mbar_init(xfree, kLutThreads);
+        mbar_init(xfull, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    int tile_lo, tile_hi;
+    if (nprob == 0) {
+        const int nt = (single.N + kTileM - 1) / kTileM;
+        tile_lo = (int)((long long)nt * blockIdx.x / gridDim.x);
+        tile_hi = (int)((long long)nt * (blockIdx.x + 1) / gridDim.x);
+    } else {
+        tile_lo = cta_first[blockIdx.x];
+        tile_hi = cta_first[blockIdx.x + 1];
+    }
+    auto problem_of = [&](int &pi, int tile) -> TaProblem {
+        if (nprob == 0) return single;
+        while (pi + 1 < nprob && tile_start[pi + 1] <= tile) ++pi;
+        return probs[pi];
+    };
+
+    const int q = warp & 3, h = warp >> 2;               // quarter of the tile's rows, which groups (g % kLutSplit == h)
+    const int r = q * 32 + lane;
+    const uint32_t tcol = sbase + S::kTab + q * (256 * 128) + lane * 4;
+    const uint32_t wring = sbase + S::kWRing + warp * (kSW * kLutStage);
+    // 16-byte piece c of this lane's row sits at piece c ^ ((lane >> 1) & 3) of the row (64-byte swizzle)
+    const uint32_t lrow = lane * 64, lkey = ((lane >> 1) & 3) << 4;
+    const uint32_t xs_u = sbase + S::kX;
+
+    // steps of this warp: one 128-code group each, groups h, h + 4, ...
+    auto open = [&](StepCursor &c) {
+        while (c.tile < tile_hi) {
+            const TaProblem p = problem_of(c.pi, c.tile);
+            c.n = ((p.K >> 7) - h + kLutSplit - 1) / kLutSplit;
+            c.x = h * 64;
+            c.y = (c.tile - p.tile0) * kTileM + q * 32;
+            c.map = nprob ? &maps[c.pi] : &single_map;
+            c.j = 0;
+            if (c.n > 0) return;
+            ++c.tile;
+        }
+    };
+    auto advance = [&](StepCursor &c) {
+        c.x += 64 * kLutSplit;
+        if (++c.j == c.n) { ++c.tile; open(c); }
+    };
+    StepCursor pf{tile_lo, 0, 0, 0, 0, 0, nullptr}, is{tile_lo, 0, 0, 0, 0, 0, nullptr};
+    int i_stage = 0;
+    auto prefetch = [&]() {
+        if (pf.tile < tile_hi) {
+            if (lane == 0) tma_2d_prefetch_l2(pf.map, pf.x, pf.y);
+            advance(pf);
+        }
+    };
+    auto issue = [&]() {
+        if (is.tile < tile_hi) {
+            if (lane == 0) {
+                const uint32_t bar = wbar(warp, i_stage);
+                mbar_expect_tx(bar, kLutStage);
+                tma_2d_g2s(wring + i_stage * kLutStage, is.map, is.x, is.y, bar);
+            }
+            advance(is);
+        }
+        i_stage = (i_stage + 1 == kSW) ? 0 : i_stage + 1;
+        prefetch();
+    };
+    open(pf);
+    open(is);
+    for (int s = 0; s < kSW + kL2Ahead; ++s) prefetch();
+#pragma unroll
+    for (int s = 0; s < kSW; ++s) issue();
+
+    uint32_t wcount = 0, qcount = 0, xcount = 0;
+    int c_pi = 0, x_pi = -1;
+    uint4 cb0 = make_uint4(0, 0, 0, 0), cb1 = cb0;
+    auto fetch_codebook = [&](int tile) {
+        if (tile < tile_hi) {
+            int pi2 = c_pi;
+            const TaProblem p = problem_of(pi2, tile);
+            const int row = min((tile - p.tile0) * kTileM + r, p.N - 1);
+            const uint4 *src = reinterpret_cast<const uint4 *>(p.codebook + (size_t)row * 16);
+            cb0 = __ldg(src);
+            cb1 = __ldg(src + 1);
+        }
+    };
+    auto quarter_sync = [&]() -> bool {
+        mbar_arrive(qbar(q));
+        const bool ok = mbar_wait(qbar(q), qcount & 1, err);
+        ++qcount;
+        return ok;
+    };
+
+#ifdef JQ_TA_PROF
+    long long lt[6] = {0, 0, 0, 0, 0, 0};
+    const long long lt0 = clock64();
+#define LT(i, expr) { const long long _t = clock64(); expr; lt[i] += clock64() - _t; }
+#else
+#define LT(i, expr) expr;
+#endif
+    fetch_codebook(tile_lo);
+    bool ok = true;
+    for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
+#ifdef JQ_TA_PROF
+        const long long _ts = clock64();
+#endif
+        const TaProblem p = problem_of(c_pi, tile);
+        const int row_raw = (tile - p.tile0) * kTileM + r;
+        const int row = min(row_raw, p.N - 1);
+        // ---- a new problem: its prepared activation replaces the previous one in shared memory
+        if (c_pi != x_pi || tile == tile_lo) {
+            mbar_arrive(xfree);                                      // this thread no longer reads the old activation
+            if (tid == 0) {
+                if ((ok = mbar_wait(xfree, xcount & 1, err))) {
+                    const uint32_t bytes = (uint32_t)p.K * B * 2;
+                    fence_async_smem();
+                    mbar_expect_tx(xfull, bytes);
+                    bulk_g2s(xs_u, p.xprep, bytes, xfull);
+                }
+            }
+            ok = mbar_wait(xfull, xcount & 1, err);
+            ++xcount;
+            x_pi = c_pi;
+            if (!ok) break;
+        }
+        // ---- the pair table of this row: this thread fills the entries whose second code is in [4 h, 4 h + 4)
+        if (!(ok = quarter_sync())) break;
+        {
+            const uint32_t c[8] = {cb0.x, cb0.y, cb0.z, cb0.w, cb1.x, cb1.y, cb1.z, cb1.w};
+            uint32_t ch[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                ch[i] = c[i];
+#pragma unroll
+                for (int hh = 1; hh < kLutSplit; ++hh) ch[i] = (h == hh) ? c[2 * hh + i] : ch[i];
+            }
+            const uint32_t tb = tcol + h * (64 * 128);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int lo = 0; lo < 16; ++lo) {
+                    const uint32_t e = __byte_perm(c[lo >> 1], ch[i >> 1],
+                                                   ((lo & 1) ? 0x32u : 0x10u) | (((i & 1) ? 0x76u : 0x54u) << 8));
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(tb + (i * 16 + lo) * 128), "r"(e) : "memory");
+                }
+        }
+        fetch_codebook(tile + 1);
+        if (!(ok = quarter_sync())) break;                           // the table is complete
+
+        float acc[B], xsc[B];
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+            acc[b] = 0.f;
+            xsc[b] = p.xscale[b];                                    // in flight during the tile, needed at its end
+        }
+        const float bias = (p.bias && row_raw < p.N) ? p.bias[row_raw] : 0.f;
+#ifdef JQ_TA_PROF
+        lt[1] += clock64() - _ts;
+#endif
+        const int nsteps = ((p.K >> 7) - h + kLutSplit - 1) / kLutSplit;
+        const unsigned short *srow = reinterpret_cast<const unsigned short *>(p.scales) + (size_t)row * p.lds;
+        const int gshift = 31 - __clz(p.g >> 7);
+        for (int j = 0; j < nsteps && ok; ++j) {
+            const int stage = wcount % kSW;
+            LT(0, ok = __all_sync(0xffffffffu, mbar_wait(wbar(warp, stage), (wcount / kSW) & 1, err)))
+            if (!ok) break;
+            ++wcount;
+            const uint32_t slot = wring + stage * kLutStage + lrow;
+            const int grp = kLutSplit * j + h;
+            const unsigned short scale_raw = __ldg(srow + (grp >> gshift));
+            const uint32_t xg0 = xs_u + (uint32_t)grp * (256 * B);   // the group's activations: [16 pieces][B][16 bytes]
+            float part[B][4];
+#pragma unroll
+            for (int b = 0; b < B; ++b) part[b][0] = part[b][1] = part[b][2] = part[b][3] = 0.f;
+#pragma unroll
+            for (int pc = 0; pc < 4; ++pc) {                         // 32 codes
+                const uint4 w4 = lds128(slot + ((pc << 4) ^ lkey));
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) {                     // 8 codes
+                    const uint32_t w = wi == 0 ? w4.x : (wi == 1 ? w4.y : (wi == 2 ? w4.z : w4.w));
+                    uint32_t v[4];
+#pragma unroll
+                    for (int bj = 0; bj < 4; ++bj) v[bj] = lds32(dp4a_u(w, 0x80u << (8 * bj), tcol));
+#pragma unroll
+                    for (int b = 0; b < B; ++b) {
+                        const uint4 xv = lds128(xg0 + (uint32_t)(((pc * 4 + wi) * B + b) * 16));
+                        fma_pair(part[b][0], part[b][1], v[0], xv.x);
+                        fma_pair(part[b][2], part[b][3], v[1], xv.y);
+                        fma_pair(part[b][0], part[b][1], v[2], xv.z);
+                        fma_pair(part[b][2], part[b][3], v[3], xv.w);
+                    }
+                }
+            }
+            const float sc = __half2float(__ushort_as_half(scale_raw));
+#pragma unroll
+            for (int b = 0; b < B; ++b)
+                acc[b] = fmaf((part[b][0] + part[b][1]) + (part[b][2] + part[b][3]), sc, acc[b]);
+            __syncwarp();
+            fence_async_smem();
+            issue();
+        }
+        if (!ok) break;
+        // ---- outputs: the other warps of the quarter hand their sums to the first through shared memory
+#ifdef JQ_TA_PROF
+        const long long _te = clock64();
+#endif
+        float *part_s = reinterpret_cast<float *>(sgen + S::kPart);
+        if (h > 0) {
+#pragma unroll
+            for (int b = 0; b < B; ++b) part_s[((h - 1) * 128 + r) * 2 + b] = acc[b];
+        }
+        if (!(ok = quarter_sync())) break;
+        if (h == 0 && row_raw < p.N) {
+#pragma unroll
+            for (int b = 0; b < B; ++b) {
+                float v = acc[b];
+#pragma unroll
+                for (int hh = 1; hh < kLutSplit; ++hh) v += part_s[((hh - 1) * 128 + r) * 2 + b];
+                const float o = fmaf(v, xsc[b], bias);
+                for (int cpy = 0; cpy < peers.n; ++cpy)
+                    jq::store_out(reinterpret_cast<char *>(p.y) + peers.delta[cpy], (size_t)b * p.ldy + row_raw, o, y_dtype);
+            }
+        }
+#ifdef JQ_TA_PROF
+        lt[2] += clock64() - _te;
+#endif
+    }
+#ifdef JQ_TA_PROF
+    lt[5] = clock64() - lt0;
+    if (blockIdx.x == 0 && lane == 0)
+        for (int i = 0; i < 6; ++i) reinterpret_cast<long long *>(status)[8 + warp * 6 + i] = lt[i];
+#endif
+    if (*err) {
+        for (int i = 0; i < 400; ++i) __nanosleep(256);
+    }
+    __syncthreads();
+    if (tid == 0 && s_err) atomicExch(status, s_err);
+}
+
+}  // namespace jqta
+
+using namespace jqta;
+
+// ---- host side -------------------------------------------------------------------
+// plan layout: 12 ints [magic, n, grid, NB, tensor-map offset (bytes), B, fmt, problem offset (bytes),
+// largest K, 0, 0, 0],
+// tile_start[n + 1], cta_first[grid + 1], padding to 64 bytes, TaProblem[n], padding to 64 bytes, CUtensorMap[n]
+static const int kTaMagic = 0x4a515441;
+static const int kTaHeader = 12;
+
+static int ta_cols(int B) { return B <= 16 ? 16 : 0; }       // MMA N
+
+static bool ta_use_lut(int B, int maxK);
+static size_t ta_align(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Tensor map over the packed rows of one matrix: bytes [N rows][ldw], boxes of 32 rows x 128 bytes with the
+// 128-byte swizzle (the CUDA-core kernel: 32 rows x 64 bytes, 64-byte swizzle); rows past N read as zeros.  The driver entry point is looked up once (no link-time
+// dependency on the driver library).
+typedef CUresult (*ta_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static ta_encode_fn ta_encoder() {
+    static ta_encode_fn fn = nullptr;
+    static bool tried = false;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<ta_encode_fn>(p);
+    }
+    return fn;
+}
+static int ta_encode_map(CUtensorMap *out, const void *qw, int N, int ldw, bool lut) {
+    ta_encode_fn enc = ta_encoder();
+    if (!enc) return JQ_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)ldw, (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldw};
+    const cuuint32_t box[2] = {lut ? 64u : 128u, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(qw), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, lut ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? JQ_OK : JQ_ERR_CUDA_BASE - (int)cudaErrorInvalidValue;
+}
+
+static bool ta_shape_ok(int fmt, int N, int K, int g, int had) {
+    if (N <= 0 || K < 512 || K % 256) return false;
+    if (had != 0 && had != 128) return false;
+    if (fmt == JQ_FMT_GF4) {
+        const int gq = g >> 7;
+        return g >= 128 && g % 128 == 0 && (gq & (gq - 1)) == 0 && K % g == 0;
+    }
+    return false;
+}
+
+// batch 1..2 run on the CUDA cores when the prepared activation of one problem fits its shared-memory buffer
+static bool ta_use_lut(int B, int maxK) { return B <= 2 && (size_t)maxK * B * 2 <= (size_t)LutSmem::kXBytes; }
+
+extern "C" size_t jq_ta_workspace_bytes(const jq_problem *ph, int n, int B) {
+    if (!ph || n <= 0 || B < 1 || !ta_cols(B)) return 0;
+    size_t total = kHeaderBytes;
+    for (int i = 0; i < n; ++i) total += 128 + ta_align((size_t)ph[i].K * B * 2, 128);
+    return total;
+}
+
+extern "C" size_t jq_ta_plan_bytes(int n) {
+    if (n <= 0) return 0;
+    return ta_align(ta_align(((size_t)kTaHeader + (size_t)(n + 1) + (size_t)jq_sm_count() + 1) * sizeof(int), 64) +
+                        (size_t)n * sizeof(TaProblem), 64) + (size_t)n * sizeof(CUtensorMap);
+}
+
+static int ta_fill_problem(TaProblem &t, int fmt, const jq_problem &p, unsigned char *ws, size_t &off, int B) {
+    if (!p.qweight || !p.x || !p.y || !p.scales) return JQ_ERR_NULL_PTR;
+    if (fmt == JQ_FMT_GF4 && !p.codebook) return JQ_ERR_NULL_PTR;
+    if (!ta_shape_ok(fmt, p.N, p.K, p.g, p.had_block)) return JQ_ERR_UNSUPPORTED;
+    if (!jq_aligned16(p.qweight) || (fmt == JQ_FMT_GF4 && !jq_aligned16(p.codebook)) ||
+        (reinterpret_cast<uintptr_t>(p.scales) & 1u))
+        return JQ_ERR_BAD_ALIGN;
+    t.qw = reinterpret_cast<const uint8_t *>(p.qweight);
+    t.scales = reinterpret_cast<const __half *>(p.scales);
+    t.codebook = reinterpret_cast<const __half *>(p.codebook);
+    t.x = p.x;
+    t.bias = p.bias;
+    t.y = p.y;
+    t.xscale = reinterpret_cast<float *>(ws + off);
+    off += 128;
+    t.xprep = reinterpret_cast<__half *>(ws + off);
+    off += ta_align((size_t)p.K * B * 2, 128);
+    t.N = p.N; t.K = p.K; t.g = p.g; t.had = p.had_block;
+    t.ldw = p.K >> 1;
+    t.lds = p.K / p.g;
+    t.ldy = p.ldy > 0 ? p.ldy : p.N;
+    t.tile0 = 0;
+    return JQ_OK;
+}
+
+extern "C" int jq_ta_plan(int fmt, const jq_problem *ph, int n, int B, void *workspace_dev, size_t workspace_bytes,
+                          void *plan_host, size_t plan_bytes) {
+    if (!ph || !plan_host || !workspace_dev) return JQ_ERR_NULL_PTR;
+    if (n <= 0 || B < 1) return JQ_ERR_BAD_SHAPE;
+    if (fmt != JQ_FMT_GF4 || !ta_cols(B)) return JQ_ERR_UNSUPPORTED;
+    if (plan_bytes < jq_ta_plan_bytes(n) || workspace_bytes < jq_ta_workspace_bytes(ph, n, B)) return JQ_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace_dev) & 127u) return JQ_ERR_BAD_ALIGN;
+    const int grid = jq_sm_count();
+    int *h = reinterpret_cast<int *>(plan_host);
+    int *tile_start = h + kTaHeader, *cta_first = tile_start + n + 1;
+    const size_t poff = ta_align(((size_t)kTaHeader + (n + 1) + grid + 1) * sizeof(int), 64);
+    const size_t moff = ta_align(poff + (size_t)n * sizeof(TaProblem), 64);
+    TaProblem *tp = reinterpret_cast<TaProblem *>(reinterpret_cast<unsigned char *>(plan_host) + poff);
+    unsigned char *maps = reinterpret_cast<unsigned char *>(plan_host) + moff;
+    size_t off = kHeaderBytes;
+    double total = 0;
+    int maxK = 0;
+    for (int i = 0; i < n; ++i) maxK = ph[i].K > maxK ? ph[i].K : maxK;
+    const bool lut = ta_use_lut(B, maxK);
+    tile_start[0] = 0;
+    for (int i = 0; i < n; ++i) {
+        int st = ta_fill_problem(tp[i], fmt, ph[i], reinterpret_cast<unsigned char *>(workspace_dev), off, B);
+        if (st) return st;
+        CUtensorMap tm;
+        st = ta_encode_map(&tm, ph[i].qweight, ph[i].N, ph[i].K >> 1, lut);
+        if (st) return st;
+        memcpy(maps + (size_t)i * sizeof(CUtensorMap), &tm, sizeof(CUtensorMap));
+        const int tiles = (ph[i].N + kTileM - 1) / kTileM;
+        tp[i].tile0 = tile_start[i];
+        tile_start[i + 1] = tile_start[i] + tiles;
+        total += (double)tiles * ph[i].K;
+    }
+    // contiguous tile ranges of (nearly) equal packed bytes: cut where the running cost passes c * total / grid
+    int cta = 0;
+    double acc = 0;
+    cta_first[0] = 0;
+    for (int i = 0; i < n; ++i)
+        for (int t = tile_start[i]; t < tile_start[i + 1]; ++t) {
+            while (cta + 1 < grid && acc + 0.5 * ph[i].K >= total * (cta + 1) / grid) cta_first[++cta] = t;
+            acc += ph[i].K;
+        }
+    while (cta < grid) cta_first[++cta] = tile_start[n];
+    h[0] = kTaMagic; h[1] = n; h[2] = grid; h[3] = ta_cols(B); h[4] = (int)moff; h[5] = B; h[6] = fmt; h[7] = (int)poff;
+    h[8] = maxK; h[9] = h[10] = h[11] = 0;
+    return JQ_OK;
+}
+
+template <int NB>
+static int ta_launch(const TaProblem *probs_dev, const CUtensorMap *maps_dev, const TaProblem &single,
+                     const CUtensorMap &single_map, int nprob, const int *tile_start,
+                     const int *cta_first, int grid, int B, int x_dtype, int y_dtype, const jqta::PeerInfo &peers,
+                     int *status, cudaStream_t st) {
+    const int nblk = (nprob ? nprob : 1) * B;
+    ta_prepare_kernel<<<nblk, 256, 0, st>>>(probs_dev, single, B, x_dtype);
+    int s = jq_launch_status();
+    if (s) return s;
+    auto kern = gemm_ta_gf4_kernel<NB>;
+    constexpr int smem = Smem::kBytes;
+    static_assert(smem <= 227 * 1024, "shared memory");
+    JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<grid, kThreads, smem, st>>>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, B, y_dtype, peers,
+                                       status);
+    return jq_launch_status();
+}
+
+template <int B>
+static int lut2_launch(const TaProblem *probs_dev, const CUtensorMap *maps_dev, const TaProblem &single,
+                       const CUtensorMap &single_map, int nprob, const int *tile_start, const int *cta_first, int grid,
+                       int x_dtype, int y_dtype, const jqta::PeerInfo &peers, int *status, cudaStream_t st) {
+    const int nblk = (nprob ? nprob : 1) * B;
+    ta_prepare_kernel<<<nblk, 256, 0, st>>>(probs_dev, single, B, x_dtype);
+    int s = jq_launch_status();
+    if (s) return s;
+    auto kern = gf4_lut2_kernel<B>;
+    constexpr int smem = LutSmem::kBytes;
+    static_assert(smem <= 227 * 1024, "shared memory");
+    JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<grid, kLutThreads, smem, st>>>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, y_dtype,
+                                          peers, status);
+    return jq_launch_status();
+}
+
+static int ta_dispatch(int nb, int maxK, const TaProblem *probs_dev, const CUtensorMap *maps_dev, const TaProblem &single,
+                       const CUtensorMap &single_map, int nprob,
+                       const int *tile_start, const int *cta_first, int grid, int B, int x_dtype, int y_dtype,
+                       const jqta::PeerInfo &peers, int *status, cudaStream_t st) {
+    if (ta_use_lut(B, maxK)) {
+        if (B == 1) return lut2_launch<1>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, x_dtype, y_dtype, peers, status, st);
+        return lut2_launch<2>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, x_dtype, y_dtype, peers, status, st);
+    }
+    if (nb == 16)
+        return ta_launch<16>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, B, x_dtype, y_dtype, peers, status, st);
+    return JQ_ERR_UNSUPPORTED;
+}
+
+extern "C" int jq_gemm_ta_grouped(const void *plan_host, const void *plan_dev, void *workspace_dev, int x_dtype,
+                                  int y_dtype, int npeer, const int64_t *peer_delta, jq_stream_t stream) {
+    if (!plan_host || !plan_dev || !workspace_dev || !peer_delta) return JQ_ERR_NULL_PTR;
+    if (npeer < 1 || npeer > 8) return JQ_ERR_BAD_SHAPE;
+    if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return JQ_ERR_BAD_DTYPE;
+    const int *h = reinterpret_cast<const int *>(plan_host);
+    if (h[0] != kTaMagic) return JQ_ERR_BAD_SHAPE;
+    jqta::PeerInfo peers;
+    peers.n = npeer;
+    for (int i = 0; i < 8; ++i) peers.delta[i] = i < npeer ? (long long)peer_delta[i] : 0;
+    const int n = h[1], grid = h[2];
+    const int *d = reinterpret_cast<const int *>(plan_dev);
+    const TaProblem *probs = reinterpret_cast<const TaProblem *>(reinterpret_cast<const unsigned char *>(plan_dev) + h[7]);
+    const CUtensorMap *maps = reinterpret_cast<const CUtensorMap *>(reinterpret_cast<const unsigned char *>(plan_dev) + h[4]);
+    if (reinterpret_cast<uintptr_t>(maps) & 63u) return JQ_ERR_BAD_ALIGN;
+    TaProblem none{};
+    CUtensorMap nomap{};
+    return ta_dispatch(h[3], h[8], probs, maps, none, nomap, n, d + kTaHeader, d + kTaHeader + n + 1, grid, h[5], x_dtype, y_dtype,
+                       peers, reinterpret_cast<int *>(workspace_dev), reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int jq_gemm_ta(int fmt, const void *qweight, const void *scales, const void *codebook, const void *x,
+                          const float *bias, void *y, int N, int K, int B, int g, int had_block, int x_dtype,
+                          int y_dtype, void *workspace, size_t workspace_bytes, jq_stream_t stream) {
+    if (!workspace) return JQ_ERR_NULL_PTR;
+    if (B < 1) return JQ_ERR_BAD_SHAPE;
+    if (fmt != JQ_FMT_GF4 || !ta_cols(B)) return JQ_ERR_UNSUPPORTED;
+    if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return JQ_ERR_BAD_DTYPE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 127u) return JQ_ERR_BAD_ALIGN;
+    jq_problem p{};
+    p.qweight = qweight; p.scales = scales; p.codebook = codebook; p.x = x; p.bias = bias; p.y = y;
+    p.N = N; p.K = K; p.g = g; p.had_block = had_block;
+    if (workspace_bytes < jq_ta_workspace_bytes(&p, 1, B)) return JQ_ERR_WORKSPACE;
+    TaProblem t;
+    size_t off = kHeaderBytes;
+    int st = ta_fill_problem(t, fmt, p, reinterpret_cast<unsigned char *>(workspace), off, B);
+    if (st) return st;
+    CUtensorMap tm;
+    st = ta_encode_map(&tm, qweight, N, K >> 1, ta_use_lut(B, K));
+    if (st) return st;
+    jqta::PeerInfo peers;
+    peers.n = 1;
+    for (int i = 0; i < 8; ++i) peers.delta[i] = 0;
+    int grid = jq_sm_count();
+    const int tiles = (N + kTileM - 1) / kTileM;
+    if (grid > tiles) grid = tiles;
+    return ta_dispatch(ta_cols(B), K, nullptr, nullptr, t, tm, 0, nullptr, nullptr, grid, B, x_dtype, y_dtype, peers,
+                       reinterpret_cast<int *>(workspace), reinterpret_cast<cudaStream_t>(stream));
+}
+
+// The status word is sticky: kernels only ever raise it.  Reading it synchronises the stream; clear != 0
+// also resets it (stream-ordered) after the read.
+extern "C" int jq_ta_status(void *workspace, int clear, jq_stream_t stream) {
+    if (!workspace) return JQ_ERR_NULL_PTR;
+    int v = 0;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    JQ_CUDA_TRY(cudaMemcpyAsync(&v, workspace, sizeof(int), cudaMemcpyDeviceToHost, st));
+    JQ_CUDA_TRY(cudaStreamSynchronize(st));
+    if (clear && v) JQ_CUDA_TRY(cudaMemsetAsync(workspace, 0, sizeof(int), st));
+    return v;
+}

@@ -19,6 +19,7 @@ from .spec import QuantSpec
 _DT = {torch.float32: _lib.JQ_F32, torch.float16: _lib.JQ_F16, torch.bfloat16: _lib.JQ_BF16}
 MAX_GEMV_BATCH = 8
 MAX_TC_BATCH = 64
+MAX_TA_BATCH = 16
 TC_MIN_BATCH = 17         # from here on E2M1 g32 goes to the tensor-core kernel (up to 16: two passes of the batch-8 loop are faster)
 _last_tc_workspace = None  # kept for status inspection (ops.tc_status())
 
@@ -72,6 +73,14 @@ def tc_eligible(fmt_id: int, K: int, g: int, batch: int) -> bool:
     return fmt_id == _lib.JQ_FMT_E2M1 and g == 32 and K % 256 == 0 and batch >= TC_MIN_BATCH
 
 
+def ta_eligible(fmt_id: int, K: int, g: int, batch: int) -> bool:
+    """GF4 problems the pair-table kernels take: batch 1..2 (CUDA-core loop) and
+    9..16 (tensor-memory kernel); in between the 16-bit-lookup MMA row loop is faster."""
+    gq = g >> 7
+    return (fmt_id == _lib.JQ_FMT_GF4 and g >= 128 and g % 128 == 0 and gq & (gq - 1) == 0 and K % g == 0
+            and K % 256 == 0 and K >= 512 and (batch <= 2 or 9 <= batch <= MAX_TA_BATCH))
+
+
 def tc_status() -> int:
     """Status word of the most recent tensor-core call (synchronises)."""
     if _last_tc_workspace is None:
@@ -88,7 +97,7 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
     key = (device, torch.cuda.current_stream(device).cuda_stream)
     t = _ws_cache.get(key)
     if t is None or t.numel() < nbytes:
-        t = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        t = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)   # (status words start at 0)
         _ws_cache[key] = t
     return t
 
@@ -107,6 +116,36 @@ def _linear_rows_tc(x2, qweight, scales, bias, N, K, had, y):
             _lib.check(st, "jq_gemm_e2m1_tc")
             _last_tc_workspace = ws
     return y
+
+
+def _linear_rows_ta(x2, qweight, scales, codebook, bias, N, K, g, had, y):
+    """GF4 through the pair-table kernels, at most MAX_TA_BATCH rows per pass."""
+    lib = _lib.load()
+    Bt = x2.shape[0]
+    prob = _lib.jq_problem()
+    prob.K = K
+    with _on(x2.device):
+        stream = _stream()
+        for b0 in range(0, Bt, MAX_TA_BATCH):
+            b1 = min(Bt, b0 + MAX_TA_BATCH)
+            wsb = lib.jq_ta_workspace_bytes(ctypes.byref(prob), 1, b1 - b0)
+            ws = _workspace(x2.device, wsb)
+            xs, ys = (x2, y) if Bt <= MAX_TA_BATCH else (x2[b0:b1], y[b0:b1])
+            st = lib.jq_gemm_ta(_lib.JQ_FMT_GF4, _ptr(qweight), _ptr(scales), _ptr(codebook), _ptr(xs), _ptr(bias),
+                                _ptr(ys), N, K, b1 - b0, g, had, _DT[x2.dtype], _DT[y.dtype], _ptr(ws), ws.numel(), stream)
+            _lib.check(st, "jq_gemm_ta")
+    return y
+
+
+def ta_status(clear: bool = True) -> int:
+    """Sticky status word of the pair-table kernels on the current device and
+    stream's workspace: 0, or a negative code if a bounded device-side wait
+    gave up since the last clearing read.  Synchronises the stream."""
+    key = (torch.device("cuda", torch.cuda.current_device()), torch.cuda.current_stream().cuda_stream)
+    ws = _ws_cache.get(key)
+    if ws is None:
+        return 0
+    return _lib.load().jq_ta_status(_ptr(ws), 1 if clear else 0, _stream())
 
 
 _wsb_cache = {}
@@ -134,6 +173,8 @@ def _linear_rows(x2, qweight, scales, codebook, bias, fmt_id, N, K, g, had, out_
     y = torch.empty((Bt, N), dtype=_OUT[out_id] or x2.dtype, device=x2.device)
     if tc_eligible(fmt_id, K, g, Bt):
         return _linear_rows_tc(x2, qweight, scales, bias, N, K, had, y)
+    if ta_eligible(fmt_id, K, g, min(Bt, MAX_TA_BATCH)) and (Bt <= 2 or Bt >= 9):
+        return _linear_rows_ta(x2, qweight, scales, codebook, bias, N, K, g, had, y)
     xd, yd = _DT[x2.dtype], _DT[y.dtype]
     qw_p, sc_p, cb_p, bias_p = _ptr(qweight), _ptr(scales), _ptr(codebook), _ptr(bias)
     with _on(x2.device):
@@ -276,10 +317,32 @@ class GroupedGemv:
         self._problems_host = arr
         self._per_problem = False
         self._subs = []
+        self._ta = []
         self._use_tc = (self._symm is None and not any(self.row_offsets) and batch <= MAX_TC_BATCH
                         and all(tc_eligible(w.spec.fmt_id, w.K, w.spec.group_size, batch) for w in weights))
         if self._use_tc:
             self.launches_per_run = None
+            return
+        self._ta = []
+        if (batch <= 2 or batch >= 9) and all(
+                ta_eligible(w.spec.fmt_id, w.K, w.spec.group_size, min(batch, 2)) for w in weights):
+            # GF4 through the pair-table kernels: one plan (and workspace) per sub-batch of at most 16 rows;
+            # a run is one activation-preparation launch plus one persistent launch per sub-batch
+            with torch.cuda.device(self.device):
+                for b0 in range(0, batch, MAX_TA_BATCH):
+                    nb = min(MAX_TA_BATCH, batch - b0)
+                    sub = (_lib.jq_problem * n)()
+                    ctypes.memmove(sub, arr, ctypes.sizeof(arr))
+                    for i, (w, nf) in enumerate(zip(weights, self.full_rows)):
+                        sub[i].x = arr[i].x + b0 * w.K * esz
+                        sub[i].y = arr[i].y + b0 * nf * esz
+                    wsb = lib.jq_ta_workspace_bytes(ctypes.byref(sub), n, nb)
+                    ws = torch.zeros(wsb, dtype=torch.uint8, device=self.device)
+                    plan_host = np.zeros((lib.jq_ta_plan_bytes(n) + 3) // 4, dtype=np.int32)
+                    _lib.check(lib.jq_ta_plan(spec0.fmt_id, ctypes.byref(sub), n, nb, _ptr(ws), wsb,
+                                              plan_host.ctypes.data, plan_host.nbytes), "jq_ta_plan")
+                    self._ta.append((plan_host, torch.from_numpy(plan_host).to(self.device), ws))
+            self.launches_per_run = 2 * len(self._ta)
             return
         # one grouped launch per sub-batch of at most 8 rows (the row loops' limit)
         with torch.cuda.device(self.device):
@@ -309,8 +372,26 @@ class GroupedGemv:
         if self._symm is not None:
             self._symm.barrier()
 
+    def status(self, clear: bool = True) -> int:
+        """Sticky device status of the pair-table kernels' workspaces (0 = fine);
+        synchronises the stream."""
+        lib = _lib.load()
+        worst = 0
+        with torch.cuda.device(self.device):
+            for _, _, ws in getattr(self, "_ta", []):
+                worst = min(worst, lib.jq_ta_status(_ptr(ws), 1 if clear else 0, _stream()))
+        return worst
+
     def run(self) -> None:
         lib = _lib.load()
+        if getattr(self, "_ta", None):
+            with torch.cuda.device(self.device):
+                for plan_host, plan_dev, ws in self._ta:
+                    st = lib.jq_gemm_ta_grouped(plan_host.ctypes.data, _ptr(plan_dev), _ptr(ws), _DT[self.x_dtype],
+                                                _DT[self.x_dtype], len(self._peer_delta), self._peer_delta.ctypes.data,
+                                                _stream())
+                    _lib.check(st, "jq_gemm_ta_grouped")
+            return
         if not self._per_problem and not self._use_tc:
             st = 0
             with torch.cuda.device(self.device):

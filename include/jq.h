@@ -222,6 +222,46 @@ int jq_gemv_grouped_peers(const jq_problem *problems_dev, const void *plan_host,
                           const void *plan_dev, int x_dtype, int y_dtype, int npeer,
                           const int64_t *peer_delta, jq_stream_t stream);
 
+/* GF4 with per-row pair tables (B200 tensor memory / TMA kernels).  Same
+ * operator as jq_gemv_gf4, i.e. the F.linear(x, W_bar, bias) of
+ * Quantization_Experiments/layers.py:38, for group sizes of 128 * 2^k,
+ * K % 256 == 0, K >= 512 and 1 <= B <= 16; every weight and scale stays exact
+ * (only the fp32 summation order differs from the other kernels).  A byte of
+ * packed codes indexes a 256-entry table of fp16 pairs that is built per
+ * 128-row tile in shared memory, one bank column per weight row, so two codes
+ * cost one conflict-free lookup; the packed rows arrive by 2-D tiled TMA.
+ *   B <= 2 : the decode threads also multiply (fma.rn.f32.f16, fp32
+ *            accumulation), reading the prepared activation by broadcast
+ *            shared-memory loads;
+ *   B >= 3 : the fp16 values go to tensor memory (tcgen05.st) as the A operand
+ *            of tcgen05.mma kind::f16, one fp32 accumulator per 128-code group,
+ *            read back (tcgen05.ld) and scaled in fp32.
+ * A launch is preceded by a small kernel that rotates, normalises and rounds
+ * the activation to fp16 once per problem (not once per CTA).  The workspace
+ * (128-byte aligned, jq_ta_workspace_bytes) holds that prepared activation and
+ * a status word at offset 0, which must be zero before the first use and is
+ * only ever raised by the kernels (a bounded device-side wait that gave up
+ * leaves JQ_ERR_TIMEOUT there and the kernel returns early with y partly
+ * written).  jq_ta_status reads it (synchronising the stream) and, with
+ * clear != 0, resets it.  Grouped form: jq_ta_plan (host only) validates the
+ * problems, creates their tensor maps and writes jq_ta_plan_bytes(n) bytes
+ * that the caller copies to the device (64-byte aligned); jq_gemm_ta_grouped
+ * enqueues the two launches, with the peer-store all-gather of
+ * jq_gemv_grouped_peers when npeer > 1.  problems_host[i].K alone is read by
+ * jq_ta_workspace_bytes. */
+size_t jq_ta_workspace_bytes(const jq_problem *problems_host, int n, int B);
+size_t jq_ta_plan_bytes(int n);
+int jq_ta_plan(int fmt, const jq_problem *problems_host, int n, int B, void *workspace_dev,
+               size_t workspace_bytes, void *plan_host, size_t plan_bytes);
+int jq_gemm_ta_grouped(const void *plan_host, const void *plan_dev, void *workspace_dev,
+                       int x_dtype, int y_dtype, int npeer, const int64_t *peer_delta,
+                       jq_stream_t stream);
+int jq_gemm_ta(int fmt, const void *qweight, const void *scales, const void *codebook,
+               const void *x, const float *bias_or_null, void *y, int N, int K, int B, int g,
+               int had_block, int x_dtype, int y_dtype, void *workspace, size_t workspace_bytes,
+               jq_stream_t stream);
+int jq_ta_status(void *workspace, int clear, jq_stream_t stream);
+
 /* n batched layers in one host call (problems_host is a HOST array whose
  * pointers are device pointers; ldy must be 0 or N): the launches are enqueued
  * back to back and share the workspace, which must be large enough for the

@@ -382,7 +382,15 @@ def test_grouped_launch_equals_single_launches(fmt, g, had, B):
     grp.run()
     torch.cuda.synchronize()
     for pw, x, y in zip(pws, grp.xs, grp.ys):
-        assert torch.equal(y, ops.linear(x, pw))
+        single = ops.linear(x, pw)
+        # a group runs in one kernel family; a single call picks the family by its own shape.  Where the
+        # two coincide the results are identical, otherwise they differ by fp32 summation order only
+        # (one bf16 rounding step at most)
+        same_family = ops.ta_eligible(pw.spec.fmt_id, pw.K, pw.spec.group_size, B) == bool(grp._ta)
+        if same_family:
+            assert torch.equal(y, single)
+        else:
+            assert (y.float() - single.float()).abs().max().item() <= 2.0 ** -7 * single.float().abs().max().item()
 
 
 @pytest.mark.parametrize("B,had", [(4, 0), (8, 128), (5, 0)])
