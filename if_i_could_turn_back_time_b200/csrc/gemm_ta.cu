@@ -679,20 +679,52 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
 // the group's fp16 scale in fp32.  At batch 1 this costs about 2.2 instructions and 0.75 shared-memory
 // wavefronts per code, where one 16-bit lookup per code costs 1.2 wavefronts; the tensor pipe, whose
 // K = 16 instructions have a floor of about 45 clocks whatever the batch, is not involved.
-constexpr int kLutSplit = 4;                         // warps that share a 32-row quarter, each taking every 4th group
-constexpr int kLutWarps = 4 * kLutSplit;
+#ifndef JQ_LUT_EXP
+#define JQ_LUT_EXP 0
+#endif
+constexpr int kLutQuarters = 2;                      // 32-row sets of a tile (each has its own pair table)
+constexpr int kLutTileM = 32 * kLutQuarters;
+constexpr int kLutSplit = 8;                         // warps that share a row set, each taking every 8th 256-code step
+constexpr int kLutWarps = kLutQuarters * kLutSplit;
 constexpr int kLutThreads = kLutWarps * 32;
-constexpr int kLutStage = 32 * 64;                   // a weight stage: 32 rows x 64 bytes (one 128-code group), 64-byte swizzle
+constexpr int kLutStage = kWStage;                   // a weight stage: 32 rows x 128 bytes (two 128-code groups), 128-byte swizzle
+constexpr int kLutSW = 2;                            // stages per warp (16 warps x 2 x 4 KB: this TMA pattern streams at 6.5 TB/s when
+                                                     // nothing else limits it; 64-byte boxes four deep reached only 4.3 TB/s)
 struct LutSmem {
     static constexpr int kTab = 0;
-    static constexpr int kWRing = kTab + kTabBytes;
-    static constexpr int kX = kWRing + kLutWarps * kSW * kLutStage;      // prepared activation of the current problem
-    static constexpr int kXBytes = 28 * 1024;
-    static constexpr int kPart = kX + kXBytes;                           // partial sums of the other warps of a quarter
-    static constexpr int kBars = kPart + (kLutSplit - 1) * 128 * 2 * 4;
-    static constexpr int kNumBars = kLutWarps * kSW + 4 + 2;             // weights, quarter sync, x free / x full
+    static constexpr int kWRing = kTab + kLutQuarters * 256 * 128;
+    static constexpr int kX = kWRing + kLutWarps * kLutSW * kLutStage;   // prepared activation of the current problem
+    static constexpr int kXBytes = 24 * 1024;
+    static constexpr int kPart = kX + kXBytes;                           // partial sums of the other warps of a row set, two tiles
+    static constexpr int kBars = kPart + 2 * (kLutSplit - 1) * kLutTileM * 2 * 4;
+    static constexpr int kNumBars = kLutWarps * kLutSW + kLutQuarters + 2;   // weights, row-set sync, x free / x full
     static constexpr int kBytes = kBars + kNumBars * 8 + 1024;
 };
+
+// The first four codes of a word decoded on the ALU pipe instead of the shared-memory pipe: the row's 16
+// fp16 entries are held as byte planes in registers (tl = low bytes, th = high bytes, entries 0-3, 4-7,
+// 8-11, 12-15); PRMT looks up four codes at once in each half of a plane (selector = the code's low three
+// bits), LOP3 picks the half by the code's bit 3 (byte masks made by a sign-replicating PRMT), and two more
+// PRMTs interleave the planes into the fp16 pairs (codes 0,1) and (2,3).
+__device__ __forceinline__ uint32_t prmt_u(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ void decode4_alu(uint32_t w, const uint32_t (&tl)[4], const uint32_t (&th)[4], uint32_t &p01,
+                                            uint32_t &p23) {
+    const uint32_t sel = w & 0x7777u;
+    uint32_t w4;
+    asm("mul.lo.u32 %0, %1, 16;" : "=r"(w4) : "r"(w));          // (a shift, on the FMA pipe)
+    const uint32_t m = prmt_u(w4, w, 0xD9C8u);                    // byte j = 0xff where code j >= 8
+    const uint32_t ll = prmt_u(tl[0], tl[1], sel), lh = prmt_u(tl[2], tl[3], sel);
+    const uint32_t hl = prmt_u(th[0], th[1], sel), hh = prmt_u(th[2], th[3], sel);
+    uint32_t lo, hi;
+    asm("lop3.b32 %0, %1, %2, %3, 0xca;" : "=r"(lo) : "r"(m), "r"(lh), "r"(ll));   // m ? lh : ll
+    asm("lop3.b32 %0, %1, %2, %3, 0xca;" : "=r"(hi) : "r"(m), "r"(hh), "r"(hl));
+    p01 = prmt_u(lo, hi, 0x5140u);
+    p23 = prmt_u(lo, hi, 0x7362u);
+}
 
 // acc0 += lo(w) * lo(x), acc1 += hi(w) * hi(x): fp16 operands, exact products, fp32 accumulation
 __device__ __forceinline__ void fma_pair(float &acc0, float &acc1, uint32_t w, uint32_t x) {
@@ -714,15 +746,15 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char *sgen = smem_raw + (sbase - smem_u32(smem_raw));
     const uint32_t bars = sbase + S::kBars;
-    auto wbar = [&](int w, int s) { return bars + 8u * (w * kSW + s); };
-    auto qbar = [&](int q) { return bars + 8u * (kLutWarps * kSW + q); };
-    const uint32_t xfree = bars + 8u * (kLutWarps * kSW + 4), xfull = xfree + 8;
+    auto wbar = [&](int w, int s) { return bars + 8u * (w * kLutSW + s); };
+    auto qbar = [&](int q) { return bars + 8u * (kLutWarps * kLutSW + q); };
+    const uint32_t xfree = bars + 8u * (kLutWarps * kLutSW + kLutQuarters), xfull = xfree + 8;
     volatile int *err = &s_err;
     if (tid == 0) {
         s_err = 0;
         for (int w = 0; w < kLutWarps; ++w)
-            for (int s = 0; s < kSW; ++s) mbar_init(wbar(w, s), 1);
-        for (int q = 0; q < 4; ++q) mbar_init(qbar(q), 32 * kLutSplit);
+            for (int s = 0; s < kLutSW; ++s) mbar_init(wbar(w, s), 1);
+        for (int q = 0; q < kLutQuarters; ++q) mbar_init(qbar(q), 32 * kLutSplit);
         mbar_init(xfree, kLutThreads);
         mbar_init(xfull, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -731,79 +763,80 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
 
     int tile_lo, tile_hi;
     if (nprob == 0) {
-        const int nt = (single.N + kTileM - 1) / kTileM;
+        const int nt = (single.N + kLutTileM - 1) / kLutTileM;
         tile_lo = (int)((long long)nt * blockIdx.x / gridDim.x);
         tile_hi = (int)((long long)nt * (blockIdx.x + 1) / gridDim.x);
     } else {
         tile_lo = cta_first[blockIdx.x];
         tile_hi = cta_first[blockIdx.x + 1];
     }
-    auto problem_of = [&](int &pi, int tile) -> TaProblem {
-        if (nprob == 0) return single;
+    // Problems change rarely along a CTA's tile sequence, so every walker keeps its current problem's fields
+    // in registers and goes back to global memory only when a tile lies beyond that problem's last tile.
+    auto problem_at = [&](int &pi, int &t_end, int tile, TaProblem &p) {
+        if (nprob == 0) { p = single; t_end = 0x7fffffff; return; }
         while (pi + 1 < nprob && tile_start[pi + 1] <= tile) ++pi;
-        return probs[pi];
+        p = probs[pi];
+        t_end = tile_start[pi + 1];
     };
 
-    const int q = warp & 3, h = warp >> 2;               // quarter of the tile's rows, which groups (g % kLutSplit == h)
+    const int q = warp % kLutQuarters, h = warp / kLutQuarters;   // row set of the tile, which groups (g % kLutSplit == h)
     const int r = q * 32 + lane;
     const uint32_t tcol = sbase + S::kTab + q * (256 * 128) + lane * 4;
-    const uint32_t wring = sbase + S::kWRing + warp * (kSW * kLutStage);
-    // 16-byte piece c of this lane's row sits at piece c ^ ((lane >> 1) & 3) of the row (64-byte swizzle)
-    const uint32_t lrow = lane * 64, lkey = ((lane >> 1) & 3) << 4;
+    const uint32_t wring = sbase + S::kWRing + warp * (kLutSW * kLutStage);
+    // 16-byte piece c of this lane's row sits at piece c ^ (lane & 7) of the row (128-byte swizzle)
+    const uint32_t lrow = lane * 128, lkey = (lane & 7) << 4;
     const uint32_t xs_u = sbase + S::kX;
 
-    // steps of this warp: one 128-code group each, groups h, h + 4, ...
-    auto open = [&](StepCursor &c) {
-        while (c.tile < tile_hi) {
-            const TaProblem p = problem_of(c.pi, c.tile);
-            c.n = ((p.K >> 7) - h + kLutSplit - 1) / kLutSplit;
-            c.x = h * 64;
-            c.y = (c.tile - p.tile0) * kTileM + q * 32;
-            c.map = nprob ? &maps[c.pi] : &single_map;
-            c.j = 0;
-            if (c.n > 0) return;
-            ++c.tile;
-        }
-    };
-    auto advance = [&](StepCursor &c) {
-        c.x += 64 * kLutSplit;
-        if (++c.j == c.n) { ++c.tile; open(c); }
-    };
-    StepCursor pf{tile_lo, 0, 0, 0, 0, 0, nullptr}, is{tile_lo, 0, 0, 0, 0, 0, nullptr};
-    int i_stage = 0;
-    auto prefetch = [&]() {
-        if (pf.tile < tile_hi) {
-            if (lane == 0) tma_2d_prefetch_l2(pf.map, pf.x, pf.y);
-            advance(pf);
+    // ---- producer side of the weight ring: steps of this warp are 256 codes each (steps h, h + 8, ... of a row)
+    int i_tile = tile_lo, i_pi = 0, i_tend = -1, i_j = 0, i_n = 0, i_x = 0, i_y = 0, i_tile0 = 0, i_steps = 0, i_stage = 0;
+    const void *i_map = nullptr;
+    auto i_open = [&]() {   // position on step 0 of tile i_tile
+        while (i_tile < tile_hi) {
+            if (i_tile >= i_tend) {
+                TaProblem p;
+                problem_at(i_pi, i_tend, i_tile, p);
+                i_steps = ((p.K >> 8) - h + kLutSplit - 1) / kLutSplit;
+                i_tile0 = p.tile0;
+                i_map = nprob ? &maps[i_pi] : &single_map;
+            }
+            i_n = i_steps;
+            i_x = h * 128;
+            i_y = (i_tile - i_tile0) * kLutTileM + q * 32;     // rows past N read as zeros
+            i_j = 0;
+            if (i_n > 0) return;
+            ++i_tile;
         }
     };
     auto issue = [&]() {
-        if (is.tile < tile_hi) {
+        if (i_tile < tile_hi) {
             if (lane == 0) {
                 const uint32_t bar = wbar(warp, i_stage);
                 mbar_expect_tx(bar, kLutStage);
-                tma_2d_g2s(wring + i_stage * kLutStage, is.map, is.x, is.y, bar);
+                tma_2d_g2s(wring + i_stage * kLutStage, i_map, i_x, i_y, bar);
             }
-            advance(is);
+            i_x += 128 * kLutSplit;
+            if (++i_j == i_n) { ++i_tile; i_open(); }
         }
-        i_stage = (i_stage + 1 == kSW) ? 0 : i_stage + 1;
-        prefetch();
+        i_stage = (i_stage + 1 == kLutSW) ? 0 : i_stage + 1;
     };
-    open(pf);
-    open(is);
-    for (int s = 0; s < kSW + kL2Ahead; ++s) prefetch();
+    i_open();
 #pragma unroll
-    for (int s = 0; s < kSW; ++s) issue();
+    for (int s = 0; s < kLutSW; ++s) issue();
 
     uint32_t wcount = 0, qcount = 0, xcount = 0;
-    int c_pi = 0, x_pi = -1;
+    // ---- the codebook of this lane's row, one tile ahead
+    int f_pi = 0, f_tend = -1, f_tile0 = 0, f_N = 1;
+    const __half *f_cb = nullptr;
     uint4 cb0 = make_uint4(0, 0, 0, 0), cb1 = cb0;
     auto fetch_codebook = [&](int tile) {
         if (tile < tile_hi) {
-            int pi2 = c_pi;
-            const TaProblem p = problem_of(pi2, tile);
-            const int row = min((tile - p.tile0) * kTileM + r, p.N - 1);
-            const uint4 *src = reinterpret_cast<const uint4 *>(p.codebook + (size_t)row * 16);
+            if (tile >= f_tend) {
+                TaProblem p;
+                problem_at(f_pi, f_tend, tile, p);
+                f_tile0 = p.tile0; f_N = p.N; f_cb = p.codebook;
+            }
+            const int row = min((tile - f_tile0) * kLutTileM + r, f_N - 1);
+            const uint4 *src = reinterpret_cast<const uint4 *>(f_cb + (size_t)row * 16);
             cb0 = __ldg(src);
             cb1 = __ldg(src + 1);
         }
@@ -815,24 +848,40 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
         return ok;
     };
 
-#ifdef JQ_TA_PROF
-    long long lt[6] = {0, 0, 0, 0, 0, 0};
-    const long long lt0 = clock64();
-#define LT(i, expr) { const long long _t = clock64(); expr; lt[i] += clock64() - _t; }
-#else
-#define LT(i, expr) expr;
-#endif
+    // ---- a finished tile whose outputs are written after the next row-set sync (first warp of the row set)
+    float *part_s = reinterpret_cast<float *>(sgen + S::kPart);      // [2 parities][kLutSplit - 1][kLutTileM][2]
+    constexpr int kPartStride = (kLutSplit - 1) * kLutTileM * 2;
+    bool have_prev = false;
+    float prev_acc[B], prev_xsc[B], prev_bias = 0.f;
+    int prev_row = 0, prev_N = 0, prev_ldy = 0;
+    void *prev_y = nullptr;
+    auto write_prev = [&](int parity) {
+        if (have_prev && h == 0 && prev_row < prev_N) {
+            const float *ps = part_s + parity * kPartStride;
+#pragma unroll
+            for (int b = 0; b < B; ++b) {
+                float v = prev_acc[b];
+#pragma unroll
+                for (int hh = 1; hh < kLutSplit; ++hh) v += ps[((hh - 1) * kLutTileM + r) * 2 + b];
+                const float o = fmaf(v, prev_xsc[b], prev_bias);
+                for (int cpy = 0; cpy < peers.n; ++cpy)
+                    jq::store_out(reinterpret_cast<char *>(prev_y) + peers.delta[cpy], (size_t)b * prev_ldy + prev_row, o, y_dtype);
+            }
+        }
+        have_prev = false;
+    };
+
+    int c_pi = 0, c_tend = -1, x_pi = -1;
+    TaProblem p = single;
     fetch_codebook(tile_lo);
     bool ok = true;
-    for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
-#ifdef JQ_TA_PROF
-        const long long _ts = clock64();
-#endif
-        const TaProblem p = problem_of(c_pi, tile);
-        const int row_raw = (tile - p.tile0) * kTileM + r;
+    int tparity = 0;
+    for (int tile = tile_lo; tile < tile_hi && ok; ++tile, tparity ^= 1) {
+        if (tile >= c_tend) problem_at(c_pi, c_tend, tile, p);
+        const int row_raw = (tile - p.tile0) * kLutTileM + r;
         const int row = min(row_raw, p.N - 1);
         // ---- a new problem: its prepared activation replaces the previous one in shared memory
-        if (c_pi != x_pi || tile == tile_lo) {
+        if (c_pi != x_pi) {
             mbar_arrive(xfree);                                      // this thread no longer reads the old activation
             if (tid == 0) {
                 if ((ok = mbar_wait(xfree, xcount & 1, err))) {
@@ -847,30 +896,38 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
             x_pi = c_pi;
             if (!ok) break;
         }
-        // ---- the pair table of this row: this thread fills the entries whose second code is in [4 h, 4 h + 4)
+        // ---- row-set sync: the previous tile's lookups are over (its table may go) and its partial sums are visible
         if (!(ok = quarter_sync())) break;
+        write_prev(tparity ^ 1);
+        // ---- the pair table of this row: this thread fills the entries whose second code is 2 h or 2 h + 1
         {
             const uint32_t c[8] = {cb0.x, cb0.y, cb0.z, cb0.w, cb1.x, cb1.y, cb1.z, cb1.w};
-            uint32_t ch[2];
+            uint32_t ch = c[0];                                      // the pair register holding entries 2 h, 2 h + 1
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                ch[i] = c[i];
+            for (int hh = 1; hh < kLutSplit; ++hh) ch = (h == hh) ? c[hh] : ch;
+            const uint32_t tb = tcol + h * (32 * 128);
 #pragma unroll
-                for (int hh = 1; hh < kLutSplit; ++hh) ch[i] = (h == hh) ? c[2 * hh + i] : ch[i];
-            }
-            const uint32_t tb = tcol + h * (64 * 128);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < 2; ++i)
 #pragma unroll
                 for (int lo = 0; lo < 16; ++lo) {
-                    const uint32_t e = __byte_perm(c[lo >> 1], ch[i >> 1],
+                    const uint32_t e = __byte_perm(c[lo >> 1], ch,
                                                    ((lo & 1) ? 0x32u : 0x10u) | (((i & 1) ? 0x76u : 0x54u) << 8));
                     asm volatile("st.shared.u32 [%0], %1;" ::"r"(tb + (i * 16 + lo) * 128), "r"(e) : "memory");
                 }
         }
+#if JQ_LUT_EXP & 1
+        // byte planes of the same codebook for the codes that are decoded on the ALU pipe
+        uint32_t tl[4], th[4];
+        {
+            const uint32_t c[8] = {cb0.x, cb0.y, cb0.z, cb0.w, cb1.x, cb1.y, cb1.z, cb1.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                tl[i] = prmt_u(c[2 * i], c[2 * i + 1], 0x6420u);
+                th[i] = prmt_u(c[2 * i], c[2 * i + 1], 0x7531u);
+            }
+        }
+#endif
         fetch_codebook(tile + 1);
-        if (!(ok = quarter_sync())) break;                           // the table is complete
-
         float acc[B], xsc[B];
 #pragma unroll
         for (int b = 0; b < B; ++b) {
@@ -878,19 +935,19 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
             xsc[b] = p.xscale[b];                                    // in flight during the tile, needed at its end
         }
         const float bias = (p.bias && row_raw < p.N) ? p.bias[row_raw] : 0.f;
-#ifdef JQ_TA_PROF
-        lt[1] += clock64() - _ts;
-#endif
-        const int nsteps = ((p.K >> 7) - h + kLutSplit - 1) / kLutSplit;
+        const int nsteps = ((p.K >> 8) - h + kLutSplit - 1) / kLutSplit;
         const unsigned short *srow = reinterpret_cast<const unsigned short *>(p.scales) + (size_t)row * p.lds;
         const int gshift = 31 - __clz(p.g >> 7);
+        if (!(ok = quarter_sync())) break;                           // the table is complete
         for (int j = 0; j < nsteps && ok; ++j) {
-            const int stage = wcount % kSW;
-            LT(0, ok = __all_sync(0xffffffffu, mbar_wait(wbar(warp, stage), (wcount / kSW) & 1, err)))
+            const int stage = wcount % kLutSW;
+            ok = __all_sync(0xffffffffu, mbar_wait(wbar(warp, stage), (wcount / kLutSW) & 1, err));
             if (!ok) break;
             ++wcount;
             const uint32_t slot = wring + stage * kLutStage + lrow;
-            const int grp = kLutSplit * j + h;
+#pragma unroll
+            for (int gi = 0; gi < 2; ++gi) {
+            const int grp = 2 * (kLutSplit * j + h) + gi;
             const unsigned short scale_raw = __ldg(srow + (grp >> gshift));
             const uint32_t xg0 = xs_u + (uint32_t)grp * (256 * B);   // the group's activations: [16 pieces][B][16 bytes]
             float part[B][4];
@@ -898,20 +955,36 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
             for (int b = 0; b < B; ++b) part[b][0] = part[b][1] = part[b][2] = part[b][3] = 0.f;
 #pragma unroll
             for (int pc = 0; pc < 4; ++pc) {                         // 32 codes
-                const uint4 w4 = lds128(slot + ((pc << 4) ^ lkey));
+                const uint4 w4 = lds128(slot + (((gi * 4 + pc) << 4) ^ lkey));
 #pragma unroll
                 for (int wi = 0; wi < 4; ++wi) {                     // 8 codes
                     const uint32_t w = wi == 0 ? w4.x : (wi == 1 ? w4.y : (wi == 2 ? w4.z : w4.w));
                     uint32_t v[4];
+#if JQ_LUT_EXP & 1
+                    decode4_alu(w, tl, th, v[0], v[1]);
+#pragma unroll
+                    for (int bj = 2; bj < 4; ++bj) v[bj] = lds32(dp4a_u(w, 0x80u << (8 * bj), tcol));
+#elif JQ_LUT_EXP & 8
+#pragma unroll
+                    for (int bj = 0; bj < 4; ++bj) v[bj] = dp4a_u(w, 0x80u << (8 * bj), tcol);
+#else
 #pragma unroll
                     for (int bj = 0; bj < 4; ++bj) v[bj] = lds32(dp4a_u(w, 0x80u << (8 * bj), tcol));
+#endif
 #pragma unroll
                     for (int b = 0; b < B; ++b) {
-                        const uint4 xv = lds128(xg0 + (uint32_t)(((pc * 4 + wi) * B + b) * 16));
-                        fma_pair(part[b][0], part[b][1], v[0], xv.x);
-                        fma_pair(part[b][2], part[b][3], v[1], xv.y);
-                        fma_pair(part[b][0], part[b][1], v[2], xv.z);
-                        fma_pair(part[b][2], part[b][3], v[3], xv.w);
+                        uint4 xv;
+                        if (JQ_LUT_EXP & 2) xv = make_uint4(w, w4.x, w4.y, 0x3c003c00u);   // no activation loads
+                        else xv = lds128(xg0 + (uint32_t)(((pc * 4 + wi) * B + b) * 16));
+                        if (JQ_LUT_EXP & 4) {   // no FMAs
+                            part[b][0] += __uint_as_float((v[0] ^ xv.x) & 0x3fffffffu);
+                            part[b][1] += __uint_as_float((v[1] ^ xv.y ^ v[2] ^ xv.z ^ v[3] ^ xv.w) & 0x3fffffffu);
+                        } else {
+                            fma_pair(part[b][0], part[b][1], v[0], xv.x);
+                            fma_pair(part[b][2], part[b][3], v[1], xv.y);
+                            fma_pair(part[b][0], part[b][1], v[2], xv.z);
+                            fma_pair(part[b][2], part[b][3], v[3], xv.w);
+                        }
                     }
                 }
             }
@@ -919,41 +992,25 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
 #pragma unroll
             for (int b = 0; b < B; ++b)
                 acc[b] = fmaf((part[b][0] + part[b][1]) + (part[b][2] + part[b][3]), sc, acc[b]);
+            }
             __syncwarp();
             fence_async_smem();
             issue();
         }
         if (!ok) break;
-        // ---- outputs: the other warps of the quarter hand their sums to the first through shared memory
-#ifdef JQ_TA_PROF
-        const long long _te = clock64();
-#endif
-        float *part_s = reinterpret_cast<float *>(sgen + S::kPart);
+        // ---- the other warps of the row set park their sums; the first keeps what it needs for the outputs
         if (h > 0) {
+            float *ps = part_s + tparity * kPartStride;
 #pragma unroll
-            for (int b = 0; b < B; ++b) part_s[((h - 1) * 128 + r) * 2 + b] = acc[b];
+            for (int b = 0; b < B; ++b) ps[((h - 1) * kLutTileM + r) * 2 + b] = acc[b];
+        } else {
+#pragma unroll
+            for (int b = 0; b < B; ++b) { prev_acc[b] = acc[b]; prev_xsc[b] = xsc[b]; }
+            prev_bias = bias; prev_row = row_raw; prev_N = p.N; prev_ldy = p.ldy; prev_y = p.y;
         }
-        if (!(ok = quarter_sync())) break;
-        if (h == 0 && row_raw < p.N) {
-#pragma unroll
-            for (int b = 0; b < B; ++b) {
-                float v = acc[b];
-#pragma unroll
-                for (int hh = 1; hh < kLutSplit; ++hh) v += part_s[((hh - 1) * 128 + r) * 2 + b];
-                const float o = fmaf(v, xsc[b], bias);
-                for (int cpy = 0; cpy < peers.n; ++cpy)
-                    jq::store_out(reinterpret_cast<char *>(p.y) + peers.delta[cpy], (size_t)b * p.ldy + row_raw, o, y_dtype);
-            }
-        }
-#ifdef JQ_TA_PROF
-        lt[2] += clock64() - _te;
-#endif
+        have_prev = true;
     }
-#ifdef JQ_TA_PROF
-    lt[5] = clock64() - lt0;
-    if (blockIdx.x == 0 && lane == 0)
-        for (int i = 0; i < 6; ++i) reinterpret_cast<long long *>(status)[8 + warp * 6 + i] = lt[i];
-#endif
+    if (ok && have_prev && (ok = quarter_sync())) write_prev(tparity ^ 1);
     if (*err) {
         for (int i = 0; i < 400; ++i) __nanosleep(256);
     }
@@ -978,7 +1035,7 @@ static bool ta_use_lut(int B, int maxK);
 static size_t ta_align(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Tensor map over the packed rows of one matrix: bytes [N rows][ldw], boxes of 32 rows x 128 bytes with the
-// 128-byte swizzle (the CUDA-core kernel: 32 rows x 64 bytes, 64-byte swizzle); rows past N read as zeros.  The driver entry point is looked up once (no link-time
+// 128-byte swizzle; rows past N read as zeros.  The driver entry point is looked up once (no link-time
 // dependency on the driver library).
 typedef CUresult (*ta_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -998,16 +1055,15 @@ static ta_encode_fn ta_encoder() {
     }
     return fn;
 }
-static int ta_encode_map(CUtensorMap *out, const void *qw, int N, int ldw, bool lut) {
+static int ta_encode_map(CUtensorMap *out, const void *qw, int N, int ldw) {
     ta_encode_fn enc = ta_encoder();
     if (!enc) return JQ_ERR_UNSUPPORTED;
     const cuuint64_t dims[2] = {(cuuint64_t)ldw, (cuuint64_t)N};
     const cuuint64_t strides[1] = {(cuuint64_t)ldw};
-    const cuuint32_t box[2] = {lut ? 64u : 128u, 32};
+    const cuuint32_t box[2] = {128, 32};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(qw), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, lut ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? JQ_OK : JQ_ERR_CUDA_BASE - (int)cudaErrorInvalidValue;
 }
@@ -1082,15 +1138,16 @@ extern "C" int jq_ta_plan(int fmt, const jq_problem *ph, int n, int B, void *wor
     int maxK = 0;
     for (int i = 0; i < n; ++i) maxK = ph[i].K > maxK ? ph[i].K : maxK;
     const bool lut = ta_use_lut(B, maxK);
+    const int tile_m = lut ? kLutTileM : kTileM;
     tile_start[0] = 0;
     for (int i = 0; i < n; ++i) {
         int st = ta_fill_problem(tp[i], fmt, ph[i], reinterpret_cast<unsigned char *>(workspace_dev), off, B);
         if (st) return st;
         CUtensorMap tm;
-        st = ta_encode_map(&tm, ph[i].qweight, ph[i].N, ph[i].K >> 1, lut);
+        st = ta_encode_map(&tm, ph[i].qweight, ph[i].N, ph[i].K >> 1);
         if (st) return st;
         memcpy(maps + (size_t)i * sizeof(CUtensorMap), &tm, sizeof(CUtensorMap));
-        const int tiles = (ph[i].N + kTileM - 1) / kTileM;
+        const int tiles = (ph[i].N + tile_m - 1) / tile_m;
         tp[i].tile0 = tile_start[i];
         tile_start[i + 1] = tile_start[i] + tiles;
         total += (double)tiles * ph[i].K;
@@ -1196,13 +1253,14 @@ extern "C" int jq_gemm_ta(int fmt, const void *qweight, const void *scales, cons
     int st = ta_fill_problem(t, fmt, p, reinterpret_cast<unsigned char *>(workspace), off, B);
     if (st) return st;
     CUtensorMap tm;
-    st = ta_encode_map(&tm, qweight, N, K >> 1, ta_use_lut(B, K));
+    st = ta_encode_map(&tm, qweight, N, K >> 1);
     if (st) return st;
     jqta::PeerInfo peers;
     peers.n = 1;
     for (int i = 0; i < 8; ++i) peers.delta[i] = 0;
     int grid = jq_sm_count();
-    const int tiles = (N + kTileM - 1) / kTileM;
+    const int tile_m = ta_use_lut(B, K) ? kLutTileM : kTileM;
+    const int tiles = (N + tile_m - 1) / tile_m;
     if (grid > tiles) grid = tiles;
     return ta_dispatch(ta_cols(B), K, nullptr, nullptr, t, tm, 0, nullptr, nullptr, grid, B, x_dtype, y_dtype, peers,
                        reinterpret_cast<int *>(workspace), reinterpret_cast<cudaStream_t>(stream));
