@@ -16,6 +16,7 @@ so it is still an ordinary ``torch.save``-able dict of tensors.
 """
 from __future__ import annotations
 
+import warnings
 from typing import Dict, Iterable, Optional
 
 import torch
@@ -31,17 +32,23 @@ _FMT = {0: "e2m1", 1: "gf4"}
 def pack_state_dict(state_dict: Dict[str, torch.Tensor], spec: QuantSpec,
                     only: Optional[Iterable[str]] = None, threads: int = 0) -> Dict[str, torch.Tensor]:
     """Float state_dict -> packed state_dict.  Every 2-D ``*.weight`` (or just
-    the prefixes in ``only``) is quantised; zeros stay zeros (the mask the
-    reference derives from them, Quantization_Experiments/utils.py:1507-1513,
-    is implicit in the packed codes)."""
+    the prefixes in ``only``) is quantised.  Without rotation, zeros stay
+    exact zeros (E2M1 code 0; GF4 pins the zero's class to 0.0), so the mask
+    the reference derives from them (Quantization_Experiments/utils.py:1507-1513)
+    is implicit in the packed codes; with ``had_block`` the rotated weight has
+    no zeros to keep.  A layer whose K is not a multiple of the group size or
+    rotation block cannot use ``spec``: it is packed as ungrouped GF4 instead,
+    with a warning, and its ``.meta`` records the format actually used."""
     only = None if only is None else set(only)
     out: Dict[str, torch.Tensor] = {}
     for key, t in state_dict.items():
         prefix = key[: -len(".weight")] if key.endswith(".weight") else None
         if prefix is not None and t.dim() == 2 and (only is None or prefix in only):
             g = spec.group_size
-            use = spec if (not g or t.shape[1] % g == 0) and (not spec.had_block or t.shape[1] % spec.had_block == 0) \
-                else QuantSpec(spec.fmt if spec.fmt == "gf4" else "gf4", 0, 0)
+            fits = (not g or t.shape[1] % g == 0) and (not spec.had_block or t.shape[1] % spec.had_block == 0)
+            use = spec if fits else QuantSpec("gf4", 0, 0)
+            if not fits:
+                warnings.warn(f"{key}: K={t.shape[1]} does not fit {spec}; packed as ungrouped GF4 instead")
             pw = pack_weight(t, use, threads=threads)
             out[prefix + ".qweight"] = pw.qweight
             if pw.scales is not None:
@@ -97,5 +104,13 @@ def load_packed_into(model: nn.Module, state_dict: Dict[str, torch.Tensor]) -> n
             for suffix in (".qweight", ".scales", ".codebook", ".meta", ".bias"):
                 rest.pop(name + suffix, None)
     if rest:
-        model.load_state_dict(rest, strict=False)
+        res = model.load_state_dict(rest, strict=False)
+        # the replaced layers have no dense weight any more; anything else missing or unknown is an error
+        replaced = {n + ".weight" for n, m in model.named_modules() if isinstance(m, JenksQuantLinear)}
+        packed_buffers = {n + s for n, m in model.named_modules() if isinstance(m, JenksQuantLinear)
+                          for s in (".qweight", ".scales", ".codebook", ".mask")}
+        missing = [k for k in res.missing_keys if k not in replaced and k not in packed_buffers]
+        if missing or res.unexpected_keys:
+            raise RuntimeError(f"packed checkpoint does not match the model: missing {missing}, "
+                               f"unexpected {list(res.unexpected_keys)}")
     return model

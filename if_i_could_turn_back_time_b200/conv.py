@@ -12,6 +12,7 @@ and the format is E2M1 g32).  groups must be 1.
 """
 from __future__ import annotations
 
+import warnings
 from typing import Optional
 
 import torch
@@ -43,8 +44,11 @@ class JenksQuantConv2d(nn.Conv2d):
         self.register_buffer("mask", mask if mask is not None else torch.ones_like(self.weight.data))
         kc = self.in_channels * self.kernel_size[0] * self.kernel_size[1]
         if group_size and kc % group_size:
-            group_size, fmt = 0, "gf4"        # reduction length not a multiple of the group: ungrouped codebook format
+            warnings.warn(f"reduction length {kc} is not a multiple of the group size {group_size}: "
+                          "this layer is packed as ungrouped GF4")
+            group_size, fmt = 0, "gf4"
         if had_block and kc % had_block:
+            warnings.warn(f"reduction length {kc} is not a multiple of the rotation block: no rotation for this layer")
             had_block = 0
         self.spec = QuantSpec(fmt, group_size, had_block)
         self.threads = threads
@@ -58,10 +62,16 @@ class JenksQuantConv2d(nn.Conv2d):
         if self.qweight is None:
             dense = self._parameters["weight"]
             W = (self.mask.to(dense.device) * dense.data).float().reshape(self.out_channels, -1)
-            pw = pack_weight(W.cpu(), self.spec, threads=self.threads).to(dense.device)
+            pw = pack_weight(W, self.spec, threads=self.threads).to(dense.device)   # on the GPU when the weight is there
             self.qweight, self.scales, self.codebook = pw.qweight, pw.scales, pw.codebook
         kc = self.in_channels * self.kernel_size[0] * self.kernel_size[1]
         return PackedWeight(self.spec, self.out_channels, kc, self.qweight, self.scales, self.codebook)
+
+    def weight_quantizer(self) -> torch.Tensor:
+        """Dense quantised weight [O, I, kh, kw], as the Conv2d branch of the
+        reference's ``replace_forward`` asks for it
+        (Quantization_Experiments/brecq.py:312-319)."""
+        return self.dequantized_weight()
 
     def dequantized_weight(self) -> torch.Tensor:
         return ops.dequantize(self.packed).reshape(self.out_channels, self.in_channels, *self.kernel_size)

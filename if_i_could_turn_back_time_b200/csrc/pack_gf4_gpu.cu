@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(kThreads, 1) pack_gf4_kernel(const float *__re
                                                                 int npad) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float *sv = reinterpret_cast<float *>(smem_raw);   // npad floats: the row being sorted
-    __shared__ int s_m, s_ke, s_breaks[kClasses + 1];
+    __shared__ int s_m, s_ke, s_zero, s_breaks[kClasses + 1];
     __shared__ float s_upper[kClasses];                // largest value of each class
     __shared__ int s_scan[kWarps + 1];
     __shared__ int s_nn[2];                            // node counts of the current and next recursion level
@@ -234,12 +234,20 @@ __global__ void __launch_bounds__(kThreads, 1) pack_gf4_kernel(const float *__re
             s_breaks[ke] = m;
             for (int j = ke; j >= 2; --j) s_breaks[j - 1] = w.arg[(size_t)j * (m + 1) + s_breaks[j]];
             s_breaks[0] = 0;
+            // index of the distinct value 0.0 (m if the row has no exact zero)
+            int lo = 0, hi = m;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (w.uv[mid] < 0.0) lo = mid + 1; else hi = mid;
+            }
+            s_zero = (lo < m && w.uv[lo] == 0.0) ? lo : m;
         }
         __syncthreads();
         if (tid < kClasses) {
             const int c = tid < ke ? tid : ke - 1;
             const int a = s_breaks[c], b = s_breaks[c + 1];
-            const double mean = __ddiv_rn(__dsub_rn(w.P1[b], w.P1[a]), __dsub_rn(w.C[b], w.C[a]));
+            double mean = __ddiv_rn(__dsub_rn(w.P1[b], w.P1[a]), __dsub_rn(w.C[b], w.C[a]));
+            if (s_zero >= a && s_zero < b) mean = 0.0;   // the class holding an exact zero is pinned to 0 (as the host packer)
             codebook[(size_t)row * kClasses + tid] = __double2half(mean);
             s_upper[tid] = tid < ke ? (float)w.uv[b - 1] : __int_as_float(0x7f800000);
         }

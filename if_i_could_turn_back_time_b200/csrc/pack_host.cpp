@@ -226,6 +226,13 @@ void gf4_row(const float *w, int K, int g, uint8_t *qrow, uint16_t *srow, uint16
         const double mean = (S.jk.P1[breaks[c + 1]] - S.jk.P1[breaks[c]]) / (S.jk.C[breaks[c + 1]] - S.jk.C[breaks[c]]);
         cbrow[c] = double_to_half_bits(mean);
     }
+    // A row with an exact zero keeps it: the class that holds the value 0 gets the entry 0.0 instead of its mean
+    // (pruned weights dequantise to exactly zero, as mask * s * (Q + Theta) does in the reference's forward).  The
+    // codebook stays ascending: the neighbouring means lie outside this class's own value range, which contains 0.
+    {
+        const auto it = std::lower_bound(S.uv.begin(), S.uv.end(), 0.0);
+        if (it != S.uv.end() && *it == 0.0) cbrow[cls_of_u[(size_t)(it - S.uv.begin())]] = 0;
+    }
     for (int c = ke; c < 16; ++c) cbrow[c] = cbrow[ke - 1];
     std::memset(qrow, 0, (size_t)stride_codes(K) / 2);
     for (int i = 0; i < K; ++i) put_code(qrow, S.order[i].second, cls_of_u[S.cls[i]]);

@@ -75,6 +75,15 @@ class JenksQuantLinear(nn.Linear):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.linear(x, self.packed, self.bias)
 
+    def weight_quantizer(self) -> torch.Tensor:
+        """The dense quantised weight, the way BRECQ-style code asks for it:
+        the reference's ``replace_forward.new_forward`` computes
+        ``F.linear(x, module.weight_quantizer(), module.bias)``
+        (Quantization_Experiments/brecq.py:321-329).  Calibration code that
+        reads W_q gets the dequantised matrix; ``attach_packed_forward`` puts
+        the fused kernel behind the same ``new_forward`` hook."""
+        return ops.dequantize(self.packed)
+
     def commit(self) -> None:
         """Pack (if not done yet) and drop the dense fp32 weight."""
         with torch.no_grad():
@@ -87,10 +96,44 @@ class JenksQuantLinear(nn.Linear):
                 f"fmt={self.spec.fmt}, group_size={self.spec.group_size}, had_block={self.spec.had_block}")
 
 
+def attach_packed_forward(module: nn.Module, quantizer) -> nn.Module:
+    """The packed counterpart of the reference's ``replace_forward``
+    (Quantization_Experiments/brecq.py:305-331) for a Linear: ``quantizer`` is
+    an AdaRound-style callable whose call returns the quantised weight W_q
+    (``AdaRoundQuantizer.forward``, brecq.py:81-92, once its rounding is
+    hard).  W_q is packed once, ``module.weight_quantizer`` keeps returning
+    the dense W_q for code that inspects it, and ``module.forward`` becomes
+    the fused kernel over the packed weight instead of ``F.linear(x, W_q,
+    bias)``.  W_q must lie on a grid the format represents exactly for the two
+    forwards to agree bit for bit; otherwise it is re-quantised by the packer.
+    Returns the module."""
+    if not isinstance(module, nn.Linear):
+        raise TypeError("attach_packed_forward handles nn.Linear modules")
+    with torch.no_grad():
+        w_q = quantizer().detach()
+    spec = getattr(module, "spec", None) or QuantSpec("gf4", 0, 0)
+    pw = pack_weight(w_q.float(), spec).to(w_q.device)
+    module.weight_quantizer = quantizer
+    module.packed_weight = pw
+
+    def new_forward(x, _m=module):
+        return ops.linear(x, _m.packed_weight, _m.bias)
+
+    module.forward = new_forward
+    return module
+
+
 def quantize_module(module, bitwidth: int = 4, **spec_kwargs):
     """Recursively replace ``nn.Linear`` layers by ``JenksQuantLinear``; the
-    mask of each layer is taken from its zero weights so sparsity survives
-    (same contract as the reference's ``quantize_module``)."""
+    mask of each layer is taken from its zero weights, as in the reference's
+    ``quantize_module`` (Quantization_Experiments/utils.py:1501-1513).  The
+    reference multiplies by the mask after quantising (layers.py:37,43); here
+    the masked weight is packed and both formats keep exact zeros: E2M1 code 0
+    is 0, and a GF4 row that contains a zero pins the codebook entry of the
+    zero's class to 0.0.  With ``had_block`` the packed weight is the rotated
+    matrix, whose entries are not zero where the original was: the rotation
+    trades the sparsity pattern for accuracy, and only the unrotated formats
+    keep pruned weights at zero."""
     if isinstance(module, JenksQuantLinear):
         return module
     if isinstance(module, nn.Linear):

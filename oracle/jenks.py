@@ -62,8 +62,13 @@ def jenks_breaks(values: np.ndarray, k: int = 16, brute: bool = False):
 def jenks_codebook_row(u: np.ndarray, k: int = 16):
     """One row of normalised values -> (codes uint8 [K], codebook fp16 [k]).
 
-    codebook[c] = fp16_rn(float64 mean of class c); entries past the classes
-    in use repeat the last mean; code = class index of the value."""
+    codebook[c] = fp16_rn(float64 mean of class c), except that when the row
+    contains an exact zero the class holding it gets the entry 0.0 (pruned
+    weights must dequantise to exactly zero, as the reference's
+    ``mask * s * (Q + Theta)`` guarantees:
+    Python_Jenks_Test/Jenks_Tests/Quantization_Experiments/layers.py:37,43);
+    the partition itself is the unconstrained optimum.  Entries past the
+    classes in use repeat the last entry; code = class index of the value."""
     u = np.asarray(u, dtype=np.float32)
     uniq, cnt, breaks = jenks_breaks(u, k)
     ke = breaks.shape[0] - 1
@@ -73,8 +78,11 @@ def jenks_codebook_row(u: np.ndarray, k: int = 16):
     means = (P1[breaks[1:]] - P1[breaks[:-1]]) / (C[breaks[1:]] - C[breaks[:-1]])
     cb = np.empty(k, dtype=np.float16)
     cb[:ke] = means.astype(np.float16)
-    cb[ke:] = cb[ke - 1]
     cls_of_uniq = np.repeat(np.arange(ke, dtype=np.uint8), np.diff(breaks))
+    z = np.searchsorted(uniq, 0.0)
+    if z < uniq.shape[0] and uniq[z] == 0.0:
+        cb[cls_of_uniq[z]] = np.float16(0.0)      # the zero class is pinned to 0 (order is kept: its neighbours' means
+    cb[ke:] = cb[ke - 1]                           # lie strictly outside the class's own range, which contains 0)
     pos = np.searchsorted(uniq, u.astype(np.float64))
     return cls_of_uniq[pos], cb
 

@@ -36,6 +36,24 @@ def load_reference_quantlinear(ref_root: str):
     return mod.QuantLinear
 
 
+def load_reference_brecq(ref_root: str):
+    """``UniformAffineQuantizer``, ``AdaRoundQuantizer`` and ``replace_forward`` of the reference's brecq.py
+    (Quantization_Experiments/brecq.py:13-92, 305-331).  The file's own imports need packages that are not
+    installed (and sibling modules on sys.path), so only these three definitions are compiled, from the
+    reference's source text, in a namespace that has torch."""
+    import ast
+    import contextlib
+    import io
+    path = os.path.join(ref_root, "Python_Jenks_Test", "Jenks_Tests", "Quantization_Experiments", "brecq.py")
+    tree = ast.parse(open(path).read())
+    want = {"UniformAffineQuantizer", "AdaRoundQuantizer", "replace_forward"}
+    body = [n for n in tree.body if isinstance(n, (ast.ClassDef, ast.FunctionDef)) and n.name in want]
+    ns = {"torch": torch, "nn": torch.nn, "F": torch.nn.functional}
+    exec(compile(ast.Module(body=body, type_ignores=[]), path, "exec"), ns)
+    ns["_quiet"] = lambda: contextlib.redirect_stdout(io.StringIO())   # the classes print while they work
+    return ns
+
+
 def ref_forward(QuantLinear, w_hat: np.ndarray, bias, x: np.ndarray) -> np.ndarray:
     N, K = w_hat.shape
     lin = torch.nn.Linear(K, N, bias=bias is not None)
@@ -126,6 +144,57 @@ def main(ref_root: str) -> None:
     w_hat = formats.dequant_gf4(c, cb, None, 0)
     np.savez_compressed(os.path.join(HERE, "lenet300_pruned_rows.npz"), W=W, x=x, qweight=formats.pack_nibbles(c),
                         codebook=cb, y=ref_forward(QL, w_hat, None, x))
+
+    # ---- all three layers of that checkpoint (97.8 % zeros): pruned weights must come back as exact zeros ----
+    Ws = [sd[f"{i}.weight"].float().numpy() for i in (1, 3, 5)]
+    bs = [sd[f"{i}.bias"].float().numpy() for i in (1, 3, 5)]
+    g = torch.Generator("cpu").manual_seed(6)
+    x = torch.rand(3, 784, generator=g).numpy()
+    out = {"x": x}
+    h = x
+    for li, (W, b) in enumerate(zip(Ws, bs)):
+        c, cb, _ = jenks.quantize_gf4(W, 0)
+        w_hat = formats.dequant_gf4(c, cb, None, 0)
+        assert np.all(w_hat[W == 0] == 0), "a pruned weight did not stay zero"
+        y = ref_forward(QL, w_hat, b, h)
+        out[f"W{li}"], out[f"b{li}"], out[f"codebook{li}"], out[f"y{li}"] = W, b, cb, y
+        out[f"codes_sha{li}"] = np.array(sha(formats.pack_nibbles(c)))
+        h = np.maximum(y, 0) if li < 2 else y
+    np.savez_compressed(os.path.join(HERE, "lenet300_pruned_layers.npz"), **out)
+
+    # ---- a half-pruned matrix with group scales: zeros survive the group normalisation too -------------------
+    g = torch.Generator("cpu").manual_seed(7)
+    W = torch.randn(16, 512, generator=g) * 0.02
+    W[torch.rand(16, 512, generator=g) < 0.5] = 0.0
+    W[3] = 0.0                                   # an all-zero row (scale guard, one distinct value)
+    W[5, :128] = 0.0                             # an all-zero group
+    W = W.numpy()
+    x = torch.randn(2, 512, generator=g).bfloat16().float().numpy()
+    c, cb, s = jenks.quantize_gf4(W, 128)
+    w_hat = formats.dequant_gf4(c, cb, s, 128)
+    assert np.all(w_hat[W == 0] == 0)
+    np.savez_compressed(os.path.join(HERE, "gf4_sparse_g128.npz"), W=W, x=x, qweight=formats.pack_nibbles(c), scales=s,
+                        codebook=cb, w_hat=w_hat, y=ref_forward(QL, w_hat, None, x))
+
+    # ---- the BRECQ boundary: a Linear whose forward the reference's replace_forward has swapped -----------------
+    bq = load_reference_brecq(ref_root)
+    g = torch.Generator("cpu").manual_seed(8)
+    lin = torch.nn.Linear(256, 48)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(48, 256, generator=g) * 0.05)
+        lin.weight[torch.rand(48, 256, generator=g) < 0.3] = 0.0       # pruned entries: AdaRound keeps them at zero
+        lin.bias.copy_(torch.randn(48, generator=g) * 0.1)
+    x = torch.randn(5, 256, generator=g)
+    with bq["_quiet"](), torch.no_grad():
+        quantizer = bq["AdaRoundQuantizer"](lin.weight.data, bq["UniformAffineQuantizer"](bitwidth=4))
+        frac = lin.weight.data / quantizer.quantizer.delta - quantizer.W_floor
+        quantizer.alpha.copy_(torch.where(frac > 0.5, torch.tensor(20.0), torch.tensor(-20.0)))   # converged: hard rounding
+        lin.weight_quantizer = quantizer
+        bq["replace_forward"](lin)
+        y = lin(x)
+        w_q = quantizer()
+    np.savez_compressed(os.path.join(HERE, "brecq_replace_forward.npz"), W=lin.weight.data.numpy(), W_q=w_q.numpy(),
+                        bias=lin.bias.data.numpy(), x=x.numpy(), y=y.numpy())
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

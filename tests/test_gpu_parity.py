@@ -366,6 +366,81 @@ def test_grouped_batched_layers_use_one_tensor_core_host_call():
         assert torch.equal(y, ops.linear(x, pw))
 
 
+# ------------------------------------------------------- BRECQ boundary ----
+def test_replace_forward_boundary_with_a_weight_quantizer(golden_dir):
+    """A Linear whose forward the reference's replace_forward has swapped for
+    F.linear(x, module.weight_quantizer(), bias) (Quantization_Experiments/brecq.py:321-329), with a converged
+    AdaRoundQuantizer (brecq.py:59-92) on a 4-bit per-row grid and pruned entries masked to zero.  The fixture
+    holds W_q and the outputs of the reference's own code; the packed forward must reproduce them."""
+    from if_i_could_turn_back_time_b200.linear import attach_packed_forward
+    z = np.load(os.path.join(golden_dir, "brecq_replace_forward.npz"))
+    lin = torch.nn.Linear(256, 48).to(DEV)
+    with torch.no_grad():
+        lin.weight.copy_(torch.from_numpy(z["W"]))
+        lin.bias.copy_(torch.from_numpy(z["bias"]))
+    w_q = torch.from_numpy(z["W_q"]).to(DEV)
+    attach_packed_forward(lin, lambda: w_q)
+    assert torch.equal(lin.weight_quantizer(), w_q)                   # calibration code still sees the dense W_q
+    w_hat = ops.dequantize(lin.packed_weight).cpu().numpy()
+    assert np.all(w_hat[z["W_q"] == 0] == 0)                          # AdaRound's mask survives packing
+    # at most 16 levels per row: every level is its own class, the codebook holds fp16(level)
+    assert np.abs(w_hat - z["W_q"]).max() <= 2.0 ** -11 * np.abs(z["W_q"]).max()
+    y = lin(torch.from_numpy(z["x"]).to(DEV)).detach().cpu().numpy()
+    assert formats.rel_err(y, z["y"]) <= TOL
+
+
+def test_quantized_modules_expose_weight_quantizer():
+    lin = torch.nn.Linear(128, 16)
+    q = jq.JenksQuantLinear(lin, 4, fmt="e2m1", group_size=32).to(DEV)
+    assert torch.equal(q.weight_quantizer(), ops.dequantize(q.packed))
+    conv = torch.nn.Conv2d(4, 8, 3)
+    qc = jq.JenksQuantConv2d(conv, 4).to(DEV)
+    assert qc.weight_quantizer().shape == conv.weight.shape
+
+
+# ------------------------------------------------ pruned weights stay zero ----
+def test_pruned_checkpoint_layers_on_the_gpu(golden_dir):
+    """The reference's pruned LeNet-300-100 checkpoint, all three layers: the
+    GPU packer reproduces the oracle's codes and codebooks, every pruned weight
+    dequantises to exactly zero on the device, and the packed 784-300-100-10
+    model reproduces the outputs of the reference's own forward."""
+    import hashlib
+    z = np.load(os.path.join(golden_dir, "lenet300_pruned_layers.npz"))
+    h = torch.from_numpy(z["x"]).to(DEV)
+    for li in range(3):
+        W = z[f"W{li}"]
+        pw = jq.pack_weight(torch.from_numpy(W).to(DEV), jq.QuantSpec("gf4", 0, 0))
+        assert hashlib.sha256(pw.qweight.cpu().numpy().tobytes()).hexdigest() == str(z[f"codes_sha{li}"])
+        assert np.array_equal(pw.codebook.cpu().numpy().view(np.uint16), z[f"codebook{li}"].view(np.uint16))
+        w_hat = ops.dequantize(pw).cpu().numpy()
+        assert np.all(w_hat[W == 0] == 0)
+        y = ops.linear(h, pw, torch.from_numpy(z[f"b{li}"]).to(DEV))
+        assert formats.rel_err(y.cpu().numpy(), z[f"y{li}"]) <= TOL
+        h = torch.relu(y) if li < 2 else y
+
+
+@pytest.mark.parametrize("B", [1, 2, 5, 12])
+def test_sparse_grouped_matrix_on_the_gpu(golden_dir, B):
+    z = np.load(os.path.join(golden_dir, "gf4_sparse_g128.npz"))
+    W = z["W"]
+    pw = jq.pack_weight(torch.from_numpy(W).to(DEV), jq.QuantSpec("gf4", 128, 0))
+    assert np.array_equal(pw.qweight.cpu().numpy(), z["qweight"])
+    assert np.array_equal(pw.codebook.cpu().numpy().view(np.uint16), z["codebook"].view(np.uint16))
+    w_hat = ops.dequantize(pw).cpu().numpy()
+    assert np.array_equal(w_hat, z["w_hat"]) and np.all(w_hat[W == 0] == 0)
+    x = torch.from_numpy(np.tile(z["x"], (6, 1))[:B]).bfloat16()
+    # unit vectors read columns of W_hat back through the GEMV: zeros come back as zeros (batch 1-2: pair-table
+    # CUDA-core kernel, 5: 16-bit-lookup MMA loop, 12: tensor-memory kernel)
+    e = torch.zeros(B, 512)
+    cols = [3 + 37 * b for b in range(B)]
+    for b, c in enumerate(cols):
+        e[b, c] = 1.0
+    y = ops.linear(e.to(DEV), pw, out_dtype=torch.float32).cpu().numpy()
+    for b, c in enumerate(cols):
+        assert np.array_equal(y[b], z["w_hat"][:, c])
+    _check_gemv(pw.to("cpu"), x)
+
+
 # ---------------------------------------------------------------- grouped ----
 @pytest.mark.parametrize("fmt,g,had,B", [("gf4", 128, 128, 1), ("e2m1", 32, 0, 2), ("gf4", 128, 128, 4),
                                          ("e2m1", 32, 128, 8), ("e2m1", 32, 0, 13), ("gf4", 128, 0, 11)])

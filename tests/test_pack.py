@@ -109,3 +109,54 @@ def test_row_shards_are_slices():
     # every quantity is per row: packing a slice equals slicing the pack
     pa = jq.pack_weight(W[:8], jq.QuantSpec("gf4", 128, 0))
     assert torch.equal(pa.qweight, a.qweight) and torch.equal(pa.scales, a.scales)
+
+
+# ------------------------------------------------------- pruned weights stay zero ----
+def _host_dequant(pw):
+    codes = formats.unpack_nibbles(pw.qweight.numpy(), pw.K)
+    s = None if pw.scales is None else pw.scales.numpy()
+    return formats.dequant_gf4(codes, pw.codebook.numpy(), s, pw.spec.group_size)
+
+
+def test_pruned_checkpoint_zeros_survive_gf4(golden_dir):
+    """All three layers of the reference's pruned LeNet-300-100 checkpoint
+    (97.8 % zeros): the class that holds an exact zero carries the entry 0.0,
+    so every pruned weight dequantises to exactly zero, as the reference's
+    mask * s * (Q + Theta) does (Quantization_Experiments/layers.py:37,43)."""
+    z = np.load(os.path.join(golden_dir, "lenet300_pruned_layers.npz"))
+    for li in range(3):
+        W = z[f"W{li}"]
+        pw = jq.pack_weight(torch.from_numpy(W), jq.QuantSpec("gf4", 0, 0))
+        assert hashlib.sha256(pw.qweight.numpy().tobytes()).hexdigest() == str(z[f"codes_sha{li}"])
+        assert np.array_equal(pw.codebook.numpy().view(np.uint16), z[f"codebook{li}"].view(np.uint16))
+        w_hat = _host_dequant(pw)
+        assert np.all(w_hat[W == 0] == 0)
+        assert np.all(np.diff(pw.codebook.numpy().astype(np.float32), axis=1) >= 0)
+
+
+def test_zeros_survive_group_scaling(golden_dir):
+    z = np.load(os.path.join(golden_dir, "gf4_sparse_g128.npz"))
+    W = z["W"]
+    pw = jq.pack_weight(torch.from_numpy(W), jq.QuantSpec("gf4", 128, 0))
+    assert np.array_equal(pw.qweight.numpy(), z["qweight"])
+    assert np.array_equal(pw.codebook.numpy().view(np.uint16), z["codebook"].view(np.uint16))
+    assert np.array_equal(pw.scales.numpy().view(np.uint16), z["scales"].view(np.uint16))
+    w_hat = _host_dequant(pw)
+    assert np.array_equal(w_hat, z["w_hat"])
+    assert np.all(w_hat[W == 0] == 0)
+
+
+@pytest.mark.parametrize("g", [0, 128])
+def test_a_few_zeros_per_row_stay_zero(g):
+    """Lightly pruned rows: the zero would otherwise share a class with small
+    non-zero neighbours and come back as their mean."""
+    rng = np.random.default_rng(3)
+    W = (rng.standard_normal((12, 512)) * 0.02).astype(np.float32)
+    W[rng.random(W.shape) < 0.01] = 0.0
+    W[0, 7] = -0.0
+    pw = jq.pack_weight(torch.from_numpy(W), jq.QuantSpec("gf4", g, 0))
+    c, cb, s = jenks.quantize_gf4(W, g)
+    _same(pw, c, s, cb)
+    w_hat = _host_dequant(pw)
+    assert (W == 0).sum() > 20 and np.all(w_hat[W == 0] == 0)
+    assert np.all(np.diff(cb.astype(np.float32), axis=1) >= 0)

@@ -7,7 +7,9 @@ or a host that passes only the layer's tensors and has no workspace to lend.
 For them the split-K partial sums live in an array built into the library.
 The test calls that entry straight through the C ABI, twice in a row with
 different inputs (the array keeps the first call's contents), and compares
-each result with the ordinary entry point that uses a caller workspace.
+each result with the ordinary entry point that uses a caller workspace (the
+two run the same kernels in the same order, so they must agree bit for bit)
+and with the CPU oracle.
 It is collected last so that a run stopping at the first failure has already
 run everything else, and it needs nothing from the other tests.
 """
@@ -41,6 +43,9 @@ def test_noalloc_matches_workspace_entry_twice(fmt, g):
     pw = jq.pack_weight(W, jq.QuantSpec(fmt, g, 128)).to(DEV)
     bias = torch.randn(N, generator=gen).to(DEV)
     fmt_id = _lib.JQ_FMT_E2M1 if fmt == "e2m1" else _lib.JQ_FMT_GF4
+    codes = formats.unpack_nibbles(pw.qweight.cpu().numpy(), K)
+    w_hat = (formats.dequant_e2m1(codes, pw.scales.cpu().numpy(), g) if fmt == "e2m1"
+             else formats.dequant_gf4(codes, pw.codebook.cpu().numpy(), pw.scales.cpu().numpy(), g))
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     for call in range(2):
         x = (torch.randn(B, K, generator=gen) * (1.0 + 3.0 * call)).bfloat16().to(DEV)
@@ -60,7 +65,9 @@ def test_noalloc_matches_workspace_entry_twice(fmt, g):
         torch.cuda.synchronize()
         a, b = y_new.cpu().numpy(), y_old.cpu().numpy()
         assert np.isfinite(a).all()
-        assert formats.rel_err(a, b) <= TOL, f"call {call}: {formats.rel_err(a, b):.3e}"
+        assert torch.equal(y_new, y_old), f"call {call}: {formats.rel_err(a, b):.3e}"
+        ref = formats.linear_ref(x.float().cpu().numpy(), w_hat, bias.cpu().numpy(), had_block=128)
+        assert formats.rel_err(a, ref) <= TOL, f"call {call} vs oracle: {formats.rel_err(a, ref):.3e}"
 
 
 def test_noalloc_rejects_problems_beyond_the_builtin_scratch():
