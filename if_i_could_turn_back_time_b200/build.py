@@ -41,10 +41,8 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False, defines=(), out: str = LIB) -> str:
-    """defines/out exist for tuning experiments (e.g. -DJQ_THREADS=1024 into
-    another file name); the default build is the product."""
-    if not force and not defines and not _stale():
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and not _stale():
         return LIB
     nvcc = _nvcc()
     objs = []
@@ -53,9 +51,7 @@ def build(force: bool = False, verbose: bool = False, defines=(), out: str = LIB
     procs = []
     for src in CUDA_SOURCES + HOST_SOURCES:
         obj = os.path.join(obj_dir, src.rsplit(".", 1)[0] + ".o")
-        if defines:
-            obj = obj[:-2] + "_x.o"
-        cmd = [nvcc, *NVCC_FLAGS, *defines, "-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose and src.endswith(".cu"):
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -66,12 +62,10 @@ def build(force: bool = False, verbose: bool = False, defines=(), out: str = LIB
             sys.stderr.write(log)
         if p.returncode:
             raise RuntimeError(f"nvcc failed on {src}")
-    cmd = [nvcc, "-shared", "-o", out, *objs, "-lcudart", "-Xcompiler", "-pthread"]
+    cmd = [nvcc, "-shared", "-o", LIB, *objs, "-lcudart", "-Xcompiler", "-pthread"]
     subprocess.check_call(cmd)
-    return out
+    return LIB
 
 
 if __name__ == "__main__":
-    defs = tuple(a for a in sys.argv[1:] if a.startswith("-D"))
-    outs = [a[len("--out="):] for a in sys.argv[1:] if a.startswith("--out=")]
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, defines=defs, out=outs[0] if outs else LIB))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

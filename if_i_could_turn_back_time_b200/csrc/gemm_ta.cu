@@ -34,7 +34,6 @@
 #include <cuda.h>
 #include <mutex>
 #include <string.h>
-#include <stdlib.h>
 
 namespace jqta {
 
@@ -45,10 +44,7 @@ constexpr int kSW = 2;                       // stages of a decode warp's weight
 constexpr int kWStage = 32 * 128;            // bytes of a weight stage: 32 rows x 128 bytes (256 codes), swizzled by TMA
 constexpr int kXRingBytes = 24 * 1024;         // activation ring: stages of max(2 KB, one 128-code chunk)
 constexpr int kXMaxStages = 12;
-#ifndef JQ_L2AHEAD
-#define JQ_L2AHEAD 6
-#endif
-constexpr int kL2Ahead = JQ_L2AHEAD;                  // steps by which the L2 prefetch runs ahead of the shared-memory fills
+constexpr int kL2Ahead = 6;                  // steps by which the L2 prefetch runs ahead of the shared-memory fills
 constexpr int kTabBytes = 4 * 256 * 128;     // GF4: 256 entries x 32 lanes x 4 bytes per 32-row quarter
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr int kHeaderBytes = 1024;           // workspace: int status
@@ -328,13 +324,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
 
     if (warp < kDecodeWarps) {
         // =============================== decode threads ===============================
-#ifdef JQ_TA_PROF
-        long long pt[6] = {0, 0, 0, 0, 0, 0};
-        const long long pt_start = clock64();
-#define PT(i, expr) { const long long _t = clock64(); expr; pt[i] += clock64() - _t; }
-#else
-#define PT(i, expr) expr;
-#endif
         const int q = warp & 3, h = warp >> 2;
         const int r = q * 32 + lane;                       // row of the tile = tensor-memory lane
         const uint32_t lane_t = tmem + ((uint32_t)(q * 32) << 16);
@@ -420,7 +409,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
         auto fold_one = [&]() -> bool {   // the oldest group in flight
             const uint32_t s = t_fold % kRing;
             bool ok;
-            PT(2, ok = __all_sync(0xffffffffu, mbar_wait(dbar(h, s), (t_fold / kRing) & 1, err)))
+            ok = __all_sync(0xffffffffu, mbar_wait(dbar(h, s), (t_fold / kRing) & 1, err));
             if (!ok) return false;
             tc_fence_after();
             unsigned short raw = raw_q[0];
@@ -431,7 +420,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
             for (int c = 0; c < NB; c += 16) {
                 uint32_t d[16];
                 tmem_ld16(lane_t + (h * kRing + s) * C::kRegion + 64 + c, d);
-                PT(3, tmem_wait_ld())
+                tmem_wait_ld();
 #pragma unroll
                 for (int i = 0; i < 16; ++i) acc[c + i] = fmaf(__uint_as_float(d[i]), pend_scale, acc[c + i]);
             }
@@ -497,7 +486,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
             const int row_raw = (tile - p.tile0) * kTileM + r;
             const int row = min(row_raw, p.N - 1);
             // ---- the pair table of this row (this thread fills the entries whose second code is in its half)
-            const long long _tb = clock64();
             if (!(ok = quarter_sync())) break;          // both warps are done with the previous tile's lookups
             {
                 const uint32_t c[8] = {cb0.x, cb0.y, cb0.z, cb0.w, cb1.x, cb1.y, cb1.z, cb1.w};
@@ -524,16 +512,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
                 acc[b] = 0.f;
                 if (h == 0) xsc[b] = b < B ? p.xscale[b] : 0.f;   // in flight during the tile, needed at its end
             }
-#ifdef JQ_TA_PROF
-            pt[4] += clock64() - _tb;
-#endif
 
             const int nsteps = ((p.K >> 8) - h + 1) >> 1;
             const unsigned short *srow = reinterpret_cast<const unsigned short *>(p.scales) + (size_t)row * p.lds;
             const int gshift = 31 - __clz(p.g >> 7);   // log2 of the 128-code groups per scale (a power of two)
             for (int j = 0; j < nsteps && ok; ++j) {
                 const int stage = wcount % kSW;
-                PT(0, ok = __all_sync(0xffffffffu, mbar_wait(wbar(warp, stage), (wcount / kSW) & 1, err)))
+                ok = __all_sync(0xffffffffu, mbar_wait(wbar(warp, stage), (wcount / kSW) & 1, err));
                 if (!ok) break;
                 ++wcount;
                 const uint32_t slot = wring + stage * kWStage + lrow;
@@ -559,7 +544,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
                     lookup16(w4[3], vb);
                     tmem_st16(a_t + 32, va);
                     tmem_st16(a_t + 48, vb);
-                    PT(1, tmem_wait_st())
+                    tmem_wait_st();
                     tc_fence_before();
                     mbar_arrive(abar(h, s));
                     ++t_h;
@@ -576,11 +561,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
             prev_row = row_raw;
         }
         if (ok) ok = finish_prev();
-#ifdef JQ_TA_PROF
-        pt[5] = clock64() - pt_start;
-        if (blockIdx.x == 0 && lane == 0)
-            for (int i = 0; i < 6; ++i) reinterpret_cast<long long *>(status)[8 + warp * 6 + i] = pt[i];
-#endif
     } else if (warp == kDecodeWarps) {
         // =============================== MMA issuer ===============================
         if (lane == 0) {
@@ -590,13 +570,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
             int pi = 0;
             bool ok = true;
             const uint32_t lbo = (uint32_t)B * 16;
-#ifdef JQ_TA_PROF
-            long long mt[4] = {0, 0, 0, 0};
-            const long long mt0 = clock64();
-#define MT(i, expr) { const long long _t = clock64(); expr; mt[i] += clock64() - _t; }
-#else
-#define MT(i, expr) expr;
-#endif
             for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
                 const TaProblem p = problem_of(pi, tile);
                 const int ng = p.K >> 7;
@@ -605,17 +578,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
                 for (int g = 0; g < ng; ++g) {
                     const int h = (g >> 1) & 1;
                     const uint32_t s = tslot[h];
-                    if (gin == 0) { MT(0, ok = mbar_wait(xbar(xs), xpar, err)) if (!ok) break; }
-                    MT(1, ok = mbar_wait(abar(h, s), tpar[h], err))
-                    if (!ok) break;
+                    if (gin == 0 && !(ok = mbar_wait(xbar(xs), xpar, err))) break;
+                    if (!(ok = mbar_wait(abar(h, s), tpar[h], err))) break;
                     tc_fence_after();
                     const uint32_t a_t = tmem + (h * kRing + s) * C::kRegion, d_t = a_t + 64;
-                    MT(2,
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         mma_f16_ts(d_t, a_t + 8 * i, smem_desc(xb + 2 * i * lbo, lbo, 128), idesc, i > 0);
-                    )
-                    MT(3, mma_commit(dbar(h, s)))
+                    mma_commit(dbar(h, s));
                     if (s + 1 == kRing) { tslot[h] = 0; tpar[h] ^= 1; } else tslot[h] = s + 1;
                     xb += xg.chunk;
                     if (++gin == xg.gps || g == ng - 1) {
@@ -626,12 +596,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
                     }
                 }
             }
-#ifdef JQ_TA_PROF
-            if (blockIdx.x == 0) {
-                for (int i = 0; i < 4; ++i) reinterpret_cast<long long *>(status)[8 + 48 + i] = mt[i];
-                reinterpret_cast<long long *>(status)[8 + 52] = clock64() - mt0;
-            }
-#endif
         }
     } else {
         // =============================== activation producer ===============================
@@ -679,9 +643,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
 // the group's fp16 scale in fp32.  At batch 1 this costs about 2.2 instructions and 0.75 shared-memory
 // wavefronts per code, where one 16-bit lookup per code costs 1.2 wavefronts; the tensor pipe, whose
 // K = 16 instructions have a floor of about 45 clocks whatever the batch, is not involved.
-#ifndef JQ_LUT_EXP
-#define JQ_LUT_EXP 0
-#endif
 constexpr int kLutQuarters = 2;                      // 32-row sets of a tile (each has its own pair table)
 constexpr int kLutTileM = 32 * kLutQuarters;
 constexpr int kLutSplit = 8;                         // warps that share a row set, each taking every 8th 256-code step
@@ -700,31 +661,6 @@ struct LutSmem {
     static constexpr int kNumBars = kLutWarps * kLutSW + kLutQuarters + 2;   // weights, row-set sync, x free / x full
     static constexpr int kBytes = kBars + kNumBars * 8 + 1024;
 };
-
-// The first four codes of a word decoded on the ALU pipe instead of the shared-memory pipe: the row's 16
-// fp16 entries are held as byte planes in registers (tl = low bytes, th = high bytes, entries 0-3, 4-7,
-// 8-11, 12-15); PRMT looks up four codes at once in each half of a plane (selector = the code's low three
-// bits), LOP3 picks the half by the code's bit 3 (byte masks made by a sign-replicating PRMT), and two more
-// PRMTs interleave the planes into the fp16 pairs (codes 0,1) and (2,3).
-__device__ __forceinline__ uint32_t prmt_u(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
-__device__ __forceinline__ void decode4_alu(uint32_t w, const uint32_t (&tl)[4], const uint32_t (&th)[4], uint32_t &p01,
-                                            uint32_t &p23) {
-    const uint32_t sel = w & 0x7777u;
-    uint32_t w4;
-    asm("mul.lo.u32 %0, %1, 16;" : "=r"(w4) : "r"(w));          // (a shift, on the FMA pipe)
-    const uint32_t m = prmt_u(w4, w, 0xD9C8u);                    // byte j = 0xff where code j >= 8
-    const uint32_t ll = prmt_u(tl[0], tl[1], sel), lh = prmt_u(tl[2], tl[3], sel);
-    const uint32_t hl = prmt_u(th[0], th[1], sel), hh = prmt_u(th[2], th[3], sel);
-    uint32_t lo, hi;
-    asm("lop3.b32 %0, %1, %2, %3, 0xca;" : "=r"(lo) : "r"(m), "r"(lh), "r"(ll));   // m ? lh : ll
-    asm("lop3.b32 %0, %1, %2, %3, 0xca;" : "=r"(hi) : "r"(m), "r"(hh), "r"(hl));
-    p01 = prmt_u(lo, hi, 0x5140u);
-    p23 = prmt_u(lo, hi, 0x7362u);
-}
 
 // acc0 += lo(w) * lo(x), acc1 += hi(w) * hi(x): fp16 operands, exact products, fp32 accumulation
 __device__ __forceinline__ void fma_pair(float &acc0, float &acc1, uint32_t w, uint32_t x) {
@@ -915,18 +851,6 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
                     asm volatile("st.shared.u32 [%0], %1;" ::"r"(tb + (i * 16 + lo) * 128), "r"(e) : "memory");
                 }
         }
-#if JQ_LUT_EXP & 1
-        // byte planes of the same codebook for the codes that are decoded on the ALU pipe
-        uint32_t tl[4], th[4];
-        {
-            const uint32_t c[8] = {cb0.x, cb0.y, cb0.z, cb0.w, cb1.x, cb1.y, cb1.z, cb1.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                tl[i] = prmt_u(c[2 * i], c[2 * i + 1], 0x6420u);
-                th[i] = prmt_u(c[2 * i], c[2 * i + 1], 0x7531u);
-            }
-        }
-#endif
         fetch_codebook(tile + 1);
         float acc[B], xsc[B];
 #pragma unroll
@@ -960,31 +884,15 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
                 for (int wi = 0; wi < 4; ++wi) {                     // 8 codes
                     const uint32_t w = wi == 0 ? w4.x : (wi == 1 ? w4.y : (wi == 2 ? w4.z : w4.w));
                     uint32_t v[4];
-#if JQ_LUT_EXP & 1
-                    decode4_alu(w, tl, th, v[0], v[1]);
-#pragma unroll
-                    for (int bj = 2; bj < 4; ++bj) v[bj] = lds32(dp4a_u(w, 0x80u << (8 * bj), tcol));
-#elif JQ_LUT_EXP & 8
-#pragma unroll
-                    for (int bj = 0; bj < 4; ++bj) v[bj] = dp4a_u(w, 0x80u << (8 * bj), tcol);
-#else
 #pragma unroll
                     for (int bj = 0; bj < 4; ++bj) v[bj] = lds32(dp4a_u(w, 0x80u << (8 * bj), tcol));
-#endif
 #pragma unroll
                     for (int b = 0; b < B; ++b) {
-                        uint4 xv;
-                        if (JQ_LUT_EXP & 2) xv = make_uint4(w, w4.x, w4.y, 0x3c003c00u);   // no activation loads
-                        else xv = lds128(xg0 + (uint32_t)(((pc * 4 + wi) * B + b) * 16));
-                        if (JQ_LUT_EXP & 4) {   // no FMAs
-                            part[b][0] += __uint_as_float((v[0] ^ xv.x) & 0x3fffffffu);
-                            part[b][1] += __uint_as_float((v[1] ^ xv.y ^ v[2] ^ xv.z ^ v[3] ^ xv.w) & 0x3fffffffu);
-                        } else {
-                            fma_pair(part[b][0], part[b][1], v[0], xv.x);
-                            fma_pair(part[b][2], part[b][3], v[1], xv.y);
-                            fma_pair(part[b][0], part[b][1], v[2], xv.z);
-                            fma_pair(part[b][2], part[b][3], v[3], xv.w);
-                        }
+                        const uint4 xv = lds128(xg0 + (uint32_t)(((pc * 4 + wi) * B + b) * 16));
+                        fma_pair(part[b][0], part[b][1], v[0], xv.x);
+                        fma_pair(part[b][2], part[b][3], v[1], xv.y);
+                        fma_pair(part[b][0], part[b][1], v[2], xv.z);
+                        fma_pair(part[b][2], part[b][3], v[3], xv.w);
                     }
                 }
             }

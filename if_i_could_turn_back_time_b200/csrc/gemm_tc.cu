@@ -23,22 +23,7 @@
 
 namespace jqtc {
 
-#ifndef JQ_TC_X
-#define JQ_TC_X 0   // timing experiments only: 1 = no MMAs, 2 = no weight copies, 4 = no epilogue reads
-#endif
-#ifdef JQ_TC_TRACE
-__device__ unsigned long long g_trace[8 * 256];   // [event][stage iteration] SM clock of CTA 0
-__device__ __forceinline__ void trace(int ev, uint32_t it) {
-    if (blockIdx.x == 0 && it < 256) { g_trace[ev * 256 + it] = (unsigned long long)clock64(); }
-}
-#define TRACE(ev, it) trace(ev, it)
-#else
-#define TRACE(ev, it)
-#endif
-#ifndef JQ_TC_PREFETCH
-#define JQ_TC_PREFETCH 12
-#endif
-constexpr int kPrefetch = JQ_TC_PREFETCH;   // stages of weights requested into L2 ahead of the shared-memory ring
+constexpr int kPrefetch = 12;   // stages of weights requested into L2 ahead of the shared-memory ring
 constexpr int kThreads = 512;   // warps 0-3 producers, 4-7 MMA issuers (4 owns tensor memory), 8-15 epilogue
 constexpr int kMmaWarps = 2;   // issuer w owns accumulator buffer w and the stages it = w, w+2, ... (warps 6, 7 idle)   // 4 service warps + 8 epilogue warps
 constexpr int kTileM = 128;
@@ -47,10 +32,7 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 
 template <int BN, int TERMS>
 struct Cfg {
-#ifndef JQ_TC_G64
-#define JQ_TC_G64 8
-#endif
-    static constexpr int G = BN >= 64 ? JQ_TC_G64 : 8;         // 32-code groups per shared-memory stage
+    static constexpr int G = 8;                                // 32-code groups per shared-memory stage
     static constexpr int SK = G * 32;                          // codes of K per stage
     // padded FP4: 16 codes per 16-byte chunk; one chunk column = 128 rows x 16 B, plus 16 B so that the 16
     // lanes that copy one row's 16 chunks do not all hit the same shared-memory bank
@@ -208,7 +190,6 @@ __global__ void __launch_bounds__(256) tc_prepare_kernel(const void *__restrict_
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     unsigned char *xq = ws + kHeaderBytes;
     int *hdr = reinterpret_cast<int *>(ws);
-    if (b == 0 && tid == 0) hdr[0] = 0;  // status word
     const bool live = b < B;
     float m = 0.f;
     if (live)
@@ -328,11 +309,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
             for (int st = 0; st < nst; ++st, ++it) {
                 const int s = it % S;
                 if (!mbar_wait(empty0 + 8 * s, ((it / S) & 1) ^ 1, err)) break;
-                if (warp == 0 && lane == 0) TRACE(0, it);
                 const uint32_t sa = smem_base + s * STAGE;
                 uint32_t dst = sa + c * C::A_CHUNK + (warp * 32 + rsub) * 16;
                 const size_t koff = (size_t)(part * nst + st) * (SK / 2) + c * 8;
-                if (c < 2 * G && !(JQ_TC_X & 2)) {
+                if (c < 2 * G) {
                     if (full_tile) {
                         const uint8_t *src = a.qw + (size_t)(tile * kTileM + warp * 32 + rsub) * ldw + koff;
                         const size_t step = (size_t)2 * ldw;
@@ -361,7 +341,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
                     else cp_async8(sa + A_BYTES + B_BYTES + r * 16, sp);
                 }
                 cp_async_arrive(full0 + 8 * s);
-                if (warp == 0 && lane == 0) TRACE(1, it);
             }
         }
     } else if (warp < 4 + kMmaWarps) {
@@ -381,16 +360,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
                     const int ab = it & 1;                 // == w: this issuer's accumulator buffer
                     uint32_t pa = (it >> 1) * ROUNDS;      // rounds this buffer has seen so far
                     if (!mbar_wait(full0 + 8 * s, (it / S) & 1, err)) break;            // tiles landed
-                    if (w == 0) TRACE(3, it);
-#ifdef JQ_TC_PROXY_FENCE
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
                     const uint32_t sa = smem_base + s * STAGE, sb = sa + A_BYTES;
 #pragma unroll
                     for (int rd = 0; rd < ROUNDS; ++rd, ++pa) {
                         if (!mbar_wait(tempty0 + 8 * ab, (pa & 1) ^ 1, err)) break;  // accumulator buffer drained
                         tc_fence_after();
-                        if (w == 0 && rd == 0) TRACE(2, it);
 #pragma unroll
                         for (int gg = 0; gg < GA; ++gg) {
                             const int g = rd * GA + gg;
@@ -398,12 +372,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
 #pragma unroll
                             for (int tk = 0; tk < TK; ++tk) {
                                 const uint64_t bd = smem_desc(sb + (g * TK + tk) * (2 * NW * 16), NW * 16, 128);
-                                if (!(JQ_TC_X & 1)) mma_f8f6f4(tmem + ab * 256 + gg * NW, ad, bd, idesc, tk > 0 ? 1u : 0u);
+                                mma_f8f6f4(tmem + ab * 256 + gg * NW, ad, bd, idesc, tk > 0 ? 1u : 0u);
                             }
                         }
                         mma_commit(tfull0 + 8 * ab);   // this round's accumulators complete
                     }
-                    if (w == 0) TRACE(4, it);
                 }
             }
         }
@@ -431,7 +404,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
                 for (int rd = 0; rd < ROUNDS; ++rd, ++pa) {
                     ok = __all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * ab, pa & 1, err));  // warp-uniform outcome
                     if (!ok) break;
-                    if (warp == 8 && lane == 0 && rd == 0) TRACE(5, it);
                     tc_fence_after();
                     const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + ab * 256 + h * CH;
                     uint32_t d[2][TN][CH];
@@ -453,7 +425,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
                     }
                     tmem_wait();
 #pragma unroll
-                    for (int gg = 0; gg < ((JQ_TC_X & 4) ? 1 : GA); ++gg) {
+                    for (int gg = 0; gg < GA; ++gg) {
                         if (gg + 1 < GA) {
 #pragma unroll
                             for (int tn = 0; tn < TN; ++tn) tmem_ld<CH>(tbase + (gg + 1) * NW + tn * BN, d[(gg + 1) & 1][tn]);
@@ -472,7 +444,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_e2m1_tc_kernel(TcArgs a) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty0 + 8 * ab);
                 }
-                if (warp == 8 && lane == 0) TRACE(6, it);
             }
             if (!ok) break;
             if (row < a.N) {
@@ -600,14 +571,17 @@ extern "C" int jq_gemm_e2m1_tc_multi(const jq_problem *problems_host, int n, int
     return JQ_OK;
 }
 
-// Status word of the last jq_gemm_e2m1_tc call that used this workspace
-// (0 = fine, JQ_ERR_TIMEOUT if a device-side wait gave up).  Synchronises the stream.
+// Status word of the jq_gemm_e2m1_tc calls that used this workspace since it was last read: 0 = fine,
+// JQ_ERR_TIMEOUT if a device-side wait gave up in any of them (kernels only raise the word, they never reset
+// it; this call clears it after reading).  The word must be zero before the workspace's first use.
+// Synchronises the stream.
 extern "C" int jq_tc_status(const void *workspace, jq_stream_t stream) {
     if (!workspace) return JQ_ERR_NULL_PTR;
     int v = 0;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     JQ_CUDA_TRY(cudaMemcpyAsync(&v, workspace, sizeof(int), cudaMemcpyDeviceToHost, st));
     JQ_CUDA_TRY(cudaStreamSynchronize(st));
+    if (v) JQ_CUDA_TRY(cudaMemsetAsync(const_cast<void *>(workspace), 0, sizeof(int), st));
     return v;
 }
 
@@ -647,9 +621,3 @@ extern "C" int jq_selftest_bounded_wait(int *status_dev, unsigned int polls, jq_
     jqtc::bounded_wait_selftest_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status_dev, polls);
     return jq_launch_status();
 }
-
-#ifdef JQ_TC_TRACE
-extern "C" int jq_tc_trace_read(unsigned long long *host_out) {
-    return cudaMemcpyFromSymbol(host_out, jqtc::g_trace, sizeof(unsigned long long) * 8 * 256) == cudaSuccess ? 0 : -1;
-}
-#endif

@@ -48,30 +48,18 @@ __host__ __device__ inline void finish_problem(GemvProblem &p) {
     p.peer_delta[0] = 0;
 }
 
-#ifndef JQ_THREADS
-#define JQ_THREADS 512
-#endif
-constexpr int kThreads = JQ_THREADS;
+constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
 
-#ifndef JQ_T_E2M1
-#define JQ_T_E2M1 4
-#endif
-#ifndef JQ_T_GF4
-#define JQ_T_GF4 4
-#endif
-#ifndef JQ_MMA_MINB_GF4
-#define JQ_MMA_MINB_GF4 3
-#endif
-#ifndef JQ_MMA_MINB
-#define JQ_MMA_MINB 2   // E2M1 batches from here up to 8 use the m16n8k16 row loop when the problem allows
-#endif
+constexpr int kRowsE2m1 = 4, kRowsGf4 = 4;   // rows a warp carries at once in the FMA row loops, batch <= 2
+constexpr int kMmaMinB = 2;                  // E2M1 batches from here up to 8 use the m16n8k16 row loop when the problem allows
+constexpr int kMmaMinBGf4 = 3;               // GF4: from 3 rows (at 2 the FMA loop's shared tables are faster)
 template <int FMT, int B>
 struct Tile {
     // rows a warp carries at once in the FMA row loops; bounded by registers and by the ring's shared memory
-    static constexpr int T = (B <= 2) ? (FMT == JQ_FMT_GF4 ? JQ_T_GF4 : JQ_T_E2M1) : (B <= 4 ? 2 : 1);
+    static constexpr int T = (B <= 2) ? (FMT == JQ_FMT_GF4 ? kRowsGf4 : kRowsE2m1) : (B <= 4 ? 2 : 1);
     // both formats have an MMA row loop for batches (GF4 from 3 rows: at 2 the FMA loop's shared tables are faster)
-    static constexpr bool kMma = B >= (FMT == JQ_FMT_GF4 ? JQ_MMA_MINB_GF4 : JQ_MMA_MINB);
+    static constexpr bool kMma = B >= (FMT == JQ_FMT_GF4 ? kMmaMinBGf4 : kMmaMinB);
     // rows of a row group, the unit in which work is handed to warps (and planned on the host)
     static constexpr int R = kMma ? 16 : T;
 };
@@ -992,9 +980,7 @@ __device__ void cta_rows_mma_gf4(const GemvProblem &p, int rg_lo, int rg_hi, con
     cp_async_wait<0>();
 }
 
-#ifndef JQ_GF4_DIRECT_MAXB
-#define JQ_GF4_DIRECT_MAXB 1
-#endif
+constexpr int kGf4DirectMaxB = 1;   // GF4 batches up to here load the packed rows straight to registers
 // the row loop that suits the problem (uniform over the CTA)
 template <int FMT, int B, int DEPTH>
 __device__ __forceinline__ void run_rows(const GemvProblem &p, int rg_lo, int rg_hi, const __half *xs, const int *sexp,
@@ -1011,7 +997,7 @@ __device__ __forceinline__ void run_rows(const GemvProblem &p, int rg_lo, int rg
     rg_lo *= kSub;
     rg_hi *= kSub;
     if (fast_scales(p)) {
-        if constexpr (FMT == JQ_FMT_GF4 && B <= JQ_GF4_DIRECT_MAXB)
+        if constexpr (FMT == JQ_FMT_GF4 && B <= kGf4DirectMaxB)
             cta_rows_gf4_direct<B, DEPTH>(p, rg_lo, rg_hi, xs, sexp, ring_base, y_dtype);
         else
             cta_rows<FMT, B, DEPTH, true>(p, rg_lo, rg_hi, xs, sexp, ring_base, y_dtype);
@@ -1402,7 +1388,7 @@ extern "C" int jq_grouped_plan(int fmt, const jq_problem *ph, int n, int B, void
     int maxK = 0, maxK_whole = 0;
     double total = 0;
     rg_start[0] = 0;
-    const bool mma_fmt = B >= (fmt == JQ_FMT_GF4 ? JQ_MMA_MINB_GF4 : JQ_MMA_MINB);
+    const bool mma_fmt = B >= (fmt == JQ_FMT_GF4 ? kMmaMinBGf4 : kMmaMinB);
     for (int i = 0; i < n; ++i) {
         int st = validate_problem(fmt, ph[i].qweight, ph[i].scales, ph[i].codebook, ph[i].x, ph[i].y, ph[i].N,
                                   ph[i].K, ph[i].g, ph[i].had_block);
@@ -1465,9 +1451,7 @@ static int launch_grouped_d(const jq_problem *pd, const int *plan_host, const in
     return jq_launch_status();
 }
 
-#ifndef JQ_TILED_DEPTH
-#define JQ_TILED_DEPTH(B) 2   // stages of the ring in a K-tiled launch: larger K tiles beat a deeper ring (decode70b, batch 8: 1142 vs 888 tok/s)
-#endif
+constexpr int kTiledDepth = 2;   // stages of the ring in a K-tiled launch: larger K tiles beat a deeper ring (decode70b, batch 8: 1142 vs 888 tok/s)
 template <int FMT, int B>
 static int launch_grouped(const jq_problem *pd, const int *plan_host, const int *plan_dev, int x_dtype, int y_dtype,
                           const PeerInfo &peers, cudaStream_t st) {
@@ -1481,7 +1465,7 @@ static int launch_grouped(const jq_problem *pd, const int *plan_host, const int 
         // whole.  (Where two stages untiled fit they are faster than three stages tiled: 3.6 vs 3.1 TB/s at
         // 16 x 8192 x 8192, batch 8.)
         if (gemv_smem_bytes<FMT, B, 2>(plan_host[3]) > kMaxSmem) {
-            constexpr int TD = JQ_TILED_DEPTH(B);
+            constexpr int TD = kTiledDepth;
             const long long xcap = ((long long)kMaxSmem - ring_bytes<FMT, B, TD>() - kSmallBytes) / 2;
             const long long tileK = ((xcap / 2) / B - kXPad) / 1024 * 1024;
             if (tileK >= 1024 && (xcap - B * (tileK + kXPad) - 8) / 2 / (16 * B) >= 1 &&

@@ -21,7 +21,6 @@ MAX_GEMV_BATCH = 8
 MAX_TC_BATCH = 64
 MAX_TA_BATCH = 16
 TC_MIN_BATCH = 17         # from here on E2M1 g32 goes to the tensor-core kernel (up to 16: two passes of the batch-8 loop are faster)
-_last_tc_workspace = None  # kept for status inspection (ops.tc_status())
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -81,40 +80,73 @@ def ta_eligible(fmt_id: int, K: int, g: int, batch: int) -> bool:
             and K % 256 == 0 and K >= 512 and (batch <= 2 or 9 <= batch <= MAX_TA_BATCH))
 
 
-def tc_status() -> int:
-    """Status word of the most recent tensor-core call (synchronises)."""
-    if _last_tc_workspace is None:
-        return 0
-    return _lib.load().jq_tc_status(_ptr(_last_tc_workspace), _stream())
-
-
 _ws_cache = {}
+_checked = False
 
 
-def _workspace(device, nbytes: int) -> torch.Tensor:
-    """Grow-only scratch per (device, stream): calls on one stream are ordered,
-    so consecutive calls may share it; another stream gets its own."""
-    key = (device, torch.cuda.current_stream(device).cuda_stream)
+def set_checked(on: bool) -> None:
+    """Checked mode: every call that runs a kernel with device-side waits (the
+    tensor-core and tensor-memory kernels) is followed by a read of its status
+    word, which synchronises the stream, and raises if a wait gave up.  Off by
+    default: the status stays in the workspace until ``check_status()``."""
+    global _checked
+    _checked = bool(on)
+
+
+def _workspace(device, nbytes: int, kind: str = "gemv") -> torch.Tensor:
+    """Grow-only scratch per (device, stream, kernel family): calls on one
+    stream are ordered, so consecutive calls may share it; another stream gets
+    its own.  The families with a status word at offset 0 ("tc", "ta") never
+    share a buffer with the split-K partial sums, and start zeroed."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream, kind)
     t = _ws_cache.get(key)
     if t is None or t.numel() < nbytes:
-        t = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)   # (status words start at 0)
+        if t is not None and kind != "gemv" and check_status(raise_on_error=False):
+            raise RuntimeError("a device-side wait gave up in an earlier call (status word raised)")
+        t = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _ws_cache[key] = t
     return t
 
 
+def check_status(raise_on_error: bool = True) -> int:
+    """Read and clear the sticky status words of this device's workspaces on
+    the current stream (synchronises).  A kernel whose bounded wait expired
+    leaves JQ_ERR_TIMEOUT there and returns early with its outputs partly
+    written; every later call keeps the word until it is read here."""
+    lib = _lib.load()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    worst = 0
+    for kind in ("tc", "ta"):
+        ws = _ws_cache.get((dev, stream, kind))
+        if ws is None:
+            continue
+        st = lib.jq_tc_status(_ptr(ws), _stream()) if kind == "tc" else lib.jq_ta_status(_ptr(ws), 1, _stream())
+        worst = min(worst, st)
+    if worst and raise_on_error:
+        raise _lib.JqError(worst, "device status")
+    return worst
+
+
+def tc_status() -> int:
+    """Status of the tensor-core kernel's calls on this stream since the last
+    read (synchronises, clears)."""
+    return check_status(raise_on_error=False)
+
+
 def _linear_rows_tc(x2, qweight, scales, bias, N, K, had, y):
-    global _last_tc_workspace
     lib = _lib.load()
     Bt = x2.shape[0]
     with torch.cuda.device(x2.device):
         for b0 in range(0, Bt, MAX_TC_BATCH):
             b1 = min(Bt, b0 + MAX_TC_BATCH)
             wsb = lib.jq_workspace_bytes(1, N, K, b1 - b0)
-            ws = _workspace(x2.device, wsb)
+            ws = _workspace(x2.device, wsb, "tc")
             st = lib.jq_gemm_e2m1_tc(_ptr(qweight), _ptr(scales), _ptr(x2[b0:b1]), _ptr(bias), _ptr(y[b0:b1]), N, K,
                                      b1 - b0, 32, had, _DT[x2.dtype], _DT[y.dtype], _ptr(ws), wsb, _stream())
             _lib.check(st, "jq_gemm_e2m1_tc")
-            _last_tc_workspace = ws
+    if _checked:
+        check_status()
     return y
 
 
@@ -129,23 +161,14 @@ def _linear_rows_ta(x2, qweight, scales, codebook, bias, N, K, g, had, y):
         for b0 in range(0, Bt, MAX_TA_BATCH):
             b1 = min(Bt, b0 + MAX_TA_BATCH)
             wsb = lib.jq_ta_workspace_bytes(ctypes.byref(prob), 1, b1 - b0)
-            ws = _workspace(x2.device, wsb)
+            ws = _workspace(x2.device, wsb, "ta")
             xs, ys = (x2, y) if Bt <= MAX_TA_BATCH else (x2[b0:b1], y[b0:b1])
             st = lib.jq_gemm_ta(_lib.JQ_FMT_GF4, _ptr(qweight), _ptr(scales), _ptr(codebook), _ptr(xs), _ptr(bias),
                                 _ptr(ys), N, K, b1 - b0, g, had, _DT[x2.dtype], _DT[y.dtype], _ptr(ws), ws.numel(), stream)
             _lib.check(st, "jq_gemm_ta")
+    if _checked:
+        check_status()
     return y
-
-
-def ta_status(clear: bool = True) -> int:
-    """Sticky status word of the pair-table kernels on the current device and
-    stream's workspace: 0, or a negative code if a bounded device-side wait
-    gave up since the last clearing read.  Synchronises the stream."""
-    key = (torch.device("cuda", torch.cuda.current_device()), torch.cuda.current_stream().cuda_stream)
-    ws = _ws_cache.get(key)
-    if ws is None:
-        return 0
-    return _lib.load().jq_ta_status(_ptr(ws), 1 if clear else 0, _stream())
 
 
 _wsb_cache = {}
@@ -380,6 +403,8 @@ class GroupedGemv:
         with torch.cuda.device(self.device):
             for _, _, ws in getattr(self, "_ta", []):
                 worst = min(worst, lib.jq_ta_status(_ptr(ws), 1 if clear else 0, _stream()))
+            if self._use_tc:
+                worst = min(worst, check_status(raise_on_error=False))
         return worst
 
     def run(self) -> None:
@@ -410,14 +435,14 @@ class GroupedGemv:
             self._per_problem = True
         if self._use_tc:
             # every matrix goes to the tensor-core kernel: one host call enqueues them all
-            global _last_tc_workspace
             wsb = max(lib.jq_workspace_bytes(1, w.N, w.K, self.batch) for w in self.weights)
-            ws = _workspace(self.device, wsb)
+            ws = _workspace(self.device, wsb, "tc")
             with torch.cuda.device(self.device):
                 st = lib.jq_gemm_e2m1_tc_multi(ctypes.byref(self._problems_host), len(self.weights), self.batch,
                                                _DT[self.x_dtype], _DT[self.x_dtype], _ptr(ws), ws.numel(), _stream())
             _lib.check(st, "jq_gemm_e2m1_tc_multi")
-            _last_tc_workspace = ws
+            if _checked:
+                check_status()
             return
         for w, x, y, b, nf, ro in zip(self.weights, self.xs, self.ys, self.biases, self.full_rows, self.row_offsets):
             y[:, ro:ro + w.N].copy_(linear(x, w, b))

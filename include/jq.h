@@ -155,17 +155,22 @@ int jq_gemv_noalloc(int fmt, const void *qweight, const void *scales_or_null,
  * normalisation per batch row (2 terms for unrotated bf16 input = exact,
  * otherwise 3 terms = 12 significant bits).  workspace must hold
  * jq_workspace_bytes(JQ_OP_GEMM_TC, N, K, B) bytes (16-byte aligned); its
- * first word receives a status (see jq_tc_status). */
+ * first word is a status (see jq_tc_status) and must be zero before the first
+ * use of the workspace. */
 int jq_gemm_e2m1_tc(const void *qweight, const void *scales, const void *x,
                     const float *bias_or_null, void *y, int N, int K, int B, int g,
                     int had_block, int x_dtype, int y_dtype, void *workspace,
                     size_t workspace_bytes, jq_stream_t stream);
 
-/* Status word the last jq_gemm_e2m1_tc on this workspace left behind: 0, or
- * JQ_ERR_TIMEOUT if a bounded device-side wait gave up (the kernel then
- * returned early; the device stays usable).  Synchronises the stream.  The
- * reference's counterpart is the blocking cudaDeviceSynchronize + launch
- * check of Python_Jenks_Test/Jenks_Tests/cuda_helpers.py:205-208. */
+/* Status word of the jq_gemm_e2m1_tc calls on this workspace since it was
+ * last read: 0, or JQ_ERR_TIMEOUT if a bounded device-side wait gave up in any
+ * of them (that kernel returned early with y partly written; the device stays
+ * usable).  The word is sticky: kernels only raise it, so a failure in one of
+ * several launches that share the workspace is not overwritten by the next;
+ * it must be zero before the workspace's first use, and this call clears it
+ * after reading.  Synchronises the stream.  The reference's counterpart is the
+ * blocking cudaDeviceSynchronize + launch check of
+ * Python_Jenks_Test/Jenks_Tests/cuda_helpers.py:205-208. */
 int jq_tc_status(const void *workspace, jq_stream_t stream);
 
 /* Self test of the failure path of the pipeline's device-side waits: one CTA

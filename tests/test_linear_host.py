@@ -63,3 +63,12 @@ def test_spec_validation():
         jq.QuantSpec("gf4", 128, 64)
     assert jq.algorithmic_bytes(jq.QuantSpec("e2m1", 32, 0), 4096, 4096, 1, 2, 2) == 9453568
     assert jq.algorithmic_bytes(jq.QuantSpec("gf4", 128, 128), 11008, 4096, 1, 2, 2) == 23631360
+
+
+def test_status_helpers_without_any_workspace():
+    """No GPU work has run: nothing to read, nothing raised; checked mode is a plain switch."""
+    from if_i_could_turn_back_time_b200 import ops
+    ops.set_checked(True)
+    assert ops._checked is True
+    ops.set_checked(False)
+    assert ops._checked is False
