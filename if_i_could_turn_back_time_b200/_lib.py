@@ -42,10 +42,6 @@ _SIGNATURES = {
                             c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "jq_gemv_noalloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                 c_int, c_int, c_int, c_int, c_int, c_void_p]),
-    "jq_gemm_e2m1_tc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
-    "jq_gemm_e2m1_tc_multi": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
-    "jq_tc_status": (c_int, [c_void_p, c_void_p]),
     "jq_ta_workspace_bytes": (c_size_t, [c_void_p, c_int, c_int]),
     "jq_ta_plan_bytes": (c_size_t, [c_int]),
     "jq_ta_plan": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p, c_size_t]),

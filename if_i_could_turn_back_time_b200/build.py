@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libjq.so")
 
-CUDA_SOURCES = ["api.cu", "dequant.cu", "gemv.cu", "gemm_tc.cu", "gemm_ta.cu", "jenks2.cu", "pack_gpu.cu", "pack_gf4_gpu.cu"]
+CUDA_SOURCES = ["api.cu", "dequant.cu", "gemv.cu", "gemm_ta.cu", "jenks2.cu", "pack_gpu.cu", "pack_gf4_gpu.cu"]
 HOST_SOURCES = ["pack_host.cpp"]
 
 NVCC_FLAGS = [

@@ -38,7 +38,6 @@
 namespace jqta {
 
 constexpr int kDecodeWarps = 8;              // warps 0-3: first half of the steps, warps 4-7: second half
-constexpr int kThreads = (kDecodeWarps + 2) * 32;   // + MMA issuer warp + activation producer warp
 constexpr int kTileM = 128;
 constexpr int kSW = 2;                       // stages of a decode warp's weight ring
 constexpr int kWStage = 32 * 128;            // bytes of a weight stage: 32 rows x 128 bytes (256 codes), swizzled by TMA
@@ -221,54 +220,59 @@ __global__ void __launch_bounds__(256) ta_prepare_kernel(const TaProblem *probs,
 }
 
 // ---- main kernel --------------------------------------------------------------------
-// tensor-memory columns: kRing regions per half (half h, slot s) of kRegion columns: A slices at +0 (64 columns
-// = one 128-code group), the group's accumulator at +64; then NB columns through which the second half's
-// threads hand their partial sums to the first half's at the end of a tile.
-constexpr int kRing = 3;                     // groups a half may have in flight (stored, not yet folded)
-template <int NB>
+// Roles of a CTA (12 warps): warps 0-7 decode (warp = 32-row quarter q of the tile x half h of the 256-code
+// steps of a row: step sg belongs to half sg & 1), warps 8 and 9 each issue the MMAs of one half (lane 0),
+// warp 10 streams the prepared activation (lane 0), warp 11 owns the tensor-memory allocation.  The two
+// halves are independent pipelines that share only the tensor pipe and the activation ring.
+//
+// Tensor-memory columns: kRing slots per half of 64 columns each for the A operand (one 128-code group);
+// GF4 adds NB accumulator columns to every slot (one accumulator per group: the group's fp16 scale is
+// applied in fp32 after tcgen05.ld), E2M1 has one accumulator of NB columns per half for the whole row
+// (its scales are folded into the fp16 weights).  NB more columns carry the second half's sums to the
+// first half's threads at the end of a tile.
+constexpr int kTaThreads = 12 * 32;
+template <int FMT, int NB>
 struct Cols {
-    static constexpr int kRegion = 64 + NB;
-    static constexpr int kExchange = 2 * kRing * kRegion;
+    static constexpr bool kGf4 = FMT == JQ_FMT_GF4;
+    static constexpr int kRing = (kGf4 || NB <= 32) ? 3 : 2;       // groups a half may have in flight
+    static constexpr int kSlot = 64 + (kGf4 ? NB : 0);
+    static constexpr int kAcc = 2 * kRing * kSlot;                 // E2M1: accumulator of half h at kAcc + h * NB
+    static constexpr int kExchange = kAcc + (kGf4 ? 0 : 2 * NB);
     static_assert(kExchange + NB <= 512, "tensor memory");
 };
 
+template <int FMT>
 struct Smem {
+    static constexpr bool kGf4 = FMT == JQ_FMT_GF4;
     static constexpr int kTab = 0;
-    static constexpr int kWRing = kTab + kTabBytes;
+    static constexpr int kWRing = kGf4 ? kTabBytes : 0;
     static constexpr int kXRing = kWRing + kDecodeWarps * kSW * kWStage;
-    static constexpr int kBars = kXRing + kXRingBytes + 512;    // + what the MMA reads past the last chunk (rows >= B)
-    static constexpr int kNumBars = kDecodeWarps * kSW + 4 * kRing + 2 * kXMaxStages + 4;   // weights, A full, D full, x full/empty, quarter sync
-    static constexpr int kBytes = kBars + kNumBars * 8 + 1024;  // + slack for the 1 KB alignment of the base (TMA swizzle)
+    static constexpr int kXBytes = kGf4 ? 24 * 1024 : 144 * 1024;   // E2M1 has no tables: room for 64 batch rows per step
+    static constexpr int kBars = kXRing + kXBytes + 512;            // + what the MMA reads past the last chunk (rows >= B)
+    static constexpr int kNumBars = kDecodeWarps * kSW + 4 * 3 + 2 * kXMaxStages + 4;   // weights, A full, MMAs done, x full/empty, quarter sync
+    static constexpr int kBytes = kBars + kNumBars * 8 + 1024;      // + slack for the 1 KB alignment of the base (TMA swizzle)
 };
 
-// geometry of the activation ring for a batch of B rows: a chunk (128 codes) is 256 B bytes; a stage holds
-// as many whole chunks as fit in 2 KB (at least one)
+// geometry of the activation ring for a batch of B rows: a step (256 codes) is 512 B bytes
 struct XGeom {
-    int chunk, gps, stage, nstages;
-    __host__ __device__ explicit XGeom(int B) {
+    int chunk, stage, nstages;
+    __host__ __device__ XGeom(int B, int ring_bytes) {
         chunk = 256 * B;
-        gps = 2048 / chunk > 0 ? 2048 / chunk : 1;
-        stage = gps * chunk;
-        nstages = kXRingBytes / stage < kXMaxStages ? kXRingBytes / stage : kXMaxStages;
+        stage = 2 * chunk;
+        nstages = ring_bytes / stage < kXMaxStages ? ring_bytes / stage : kXMaxStages;
     }
 };
 
-// A thread's walk over its (tile, step) pairs: used three times per decode thread (L2 prefetch, shared-memory
-// fill, consumption), each a fixed distance behind the previous one.
-struct StepCursor {
-    int tile, pi, j, n;
-    int x, y;               // byte offset in the packed row, first row of the warp's 32
-    const void *map;
-};
-
-template <int NB>
-__global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProblem *probs, const CUtensorMap *maps,
-                                                                   const __grid_constant__ TaProblem single,
-                                                                   const __grid_constant__ CUtensorMap single_map, int nprob,
-                                                                   const int *tile_start, const int *cta_first,
-                                                                   int B, int y_dtype, PeerInfo peers, int *status) {
-    using C = Cols<NB>;
-    using S = Smem;
+template <int FMT, int NB>
+__global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem *probs, const CUtensorMap *maps,
+                                                                const __grid_constant__ TaProblem single,
+                                                                const __grid_constant__ CUtensorMap single_map, int nprob,
+                                                                const int *tile_start, const int *cta_first,
+                                                                int B, int y_dtype, PeerInfo peers, int *status) {
+    using C = Cols<FMT, NB>;
+    using S = Smem<FMT>;
+    constexpr bool kGf4 = FMT == JQ_FMT_GF4;
+    constexpr int kRing = C::kRing;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
@@ -276,28 +280,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bars = sbase + S::kBars;
     auto wbar = [&](int w, int s) { return bars + 8u * (w * kSW + s); };
-    auto abar = [&](int h, int s) { return bars + 8u * (kDecodeWarps * kSW + h * kRing + s); };
-    auto dbar = [&](int h, int s) { return bars + 8u * (kDecodeWarps * kSW + 2 * kRing + h * kRing + s); };
-    auto xbar = [&](int s) { return bars + 8u * (kDecodeWarps * kSW + 4 * kRing + s); };
-    auto xebar = [&](int s) { return bars + 8u * (kDecodeWarps * kSW + 4 * kRing + kXMaxStages + s); };
-    auto qbar = [&](int q) { return bars + 8u * (kDecodeWarps * kSW + 4 * kRing + 2 * kXMaxStages + q); };
+    auto abar = [&](int h, int s) { return bars + 8u * (kDecodeWarps * kSW + h * 3 + s); };
+    auto dbar = [&](int h, int s) { return bars + 8u * (kDecodeWarps * kSW + 6 + h * 3 + s); };
+    auto xbar = [&](int s) { return bars + 8u * (kDecodeWarps * kSW + 12 + s); };
+    auto xebar = [&](int s) { return bars + 8u * (kDecodeWarps * kSW + 12 + kXMaxStages + s); };
+    auto qbar = [&](int q) { return bars + 8u * (kDecodeWarps * kSW + 12 + 2 * kXMaxStages + q); };
     volatile int *err = &s_err;
-    const XGeom xg(B);
+    const XGeom xg(B, S::kXBytes);
 
     if (tid == 0) {
         s_err = 0;
         for (int w = 0; w < kDecodeWarps; ++w)
             for (int s = 0; s < kSW; ++s) mbar_init(wbar(w, s), 1);     // one arrive.expect_tx per fill
         for (int h = 0; h < 2; ++h)
-            for (int s = 0; s < kRing; ++s) {
+            for (int s = 0; s < 3; ++s) {
                 mbar_init(abar(h, s), 128);                             // the 128 decode threads of the half
                 mbar_init(dbar(h, s), 1);                               // one tcgen05.commit
             }
         for (int s = 0; s < kXMaxStages; ++s) { mbar_init(xbar(s), 1); mbar_init(xebar(s), 1); }
-        for (int q = 0; q < 4; ++q) mbar_init(qbar(q), 64);             // the two warps that share a table quarter
+        for (int q = 0; q < 4; ++q) mbar_init(qbar(q), 64);             // the two warps that share a quarter of the rows
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == kDecodeWarps) {
+    if (warp == 11) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -316,10 +320,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
         tile_lo = cta_first[blockIdx.x];
         tile_hi = cta_first[blockIdx.x + 1];
     }
-    auto problem_of = [&](int &pi, int tile) -> TaProblem {
-        if (nprob == 0) return single;
+    // Problems change rarely along a CTA's tile sequence: every walker keeps what it needs of its current
+    // problem in registers and goes back to global memory only for a tile beyond that problem's last one.
+    auto problem_at = [&](int &pi, int &t_end, int tile, TaProblem &p) {
+        if (nprob == 0) { p = single; t_end = 0x7fffffff; return; }
         while (pi + 1 < nprob && tile_start[pi + 1] <= tile) ++pi;
-        return probs[pi];
+        p = probs[pi];
+        t_end = tile_start[pi + 1];
     };
 
     if (warp < kDecodeWarps) {
@@ -327,102 +334,103 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
         const int q = warp & 3, h = warp >> 2;
         const int r = q * 32 + lane;                       // row of the tile = tensor-memory lane
         const uint32_t lane_t = tmem + ((uint32_t)(q * 32) << 16);
-        const uint32_t tcol = sbase + S::kTab + q * (256 * 128) + lane * 4;   // entry e of this row at tcol + 128 e
+        const uint32_t tcol = sbase + S::kTab + q * (256 * 128) + lane * 4;   // GF4: entry e of this row at tcol + 128 e
         const uint32_t wring = sbase + S::kWRing + warp * (kSW * kWStage);     // + stage * kWStage; 1 KB aligned
         // 16-byte piece c of this lane's row sits at piece c ^ (lane & 7) of the row (128-byte swizzle)
         const uint32_t lrow = lane * 128, lkey = (lane & 7) << 4;
 
-        // position a cursor on step 0 of its tile (skipping tiles in which this half has no step)
-        auto open = [&](StepCursor &c) {
-            while (c.tile < tile_hi) {
-                const TaProblem p = problem_of(c.pi, c.tile);
-                c.n = ((p.K >> 8) - h + 1) >> 1;
-                c.x = h * 128;
-                c.y = (c.tile - p.tile0) * kTileM + q * 32;     // rows past N read as zeros
-                c.map = nprob ? &maps[c.pi] : &single_map;
-                c.j = 0;
-                if (c.n > 0) return;
-                ++c.tile;
-            }
-        };
-        auto advance = [&](StepCursor &c) {
-            c.x += 256;
-            if (++c.j == c.n) { ++c.tile; open(c); }
-        };
-        StepCursor pf{tile_lo, 0, 0, 0, 0, 0, nullptr}, is{tile_lo, 0, 0, 0, 0, 0, nullptr};
-        int i_stage = 0;
-        auto prefetch = [&]() {     // the box of a later step, into L2
-            if (pf.tile < tile_hi) {
-                if (lane == 0) tma_2d_prefetch_l2(pf.map, pf.x, pf.y);
-                advance(pf);
+        // ---- producer side of the weight ring: the (tile, step) whose box is requested next
+        int i_tile = tile_lo, i_pi = 0, i_tend = -1, i_j = 0, i_n = 0, i_x = 0, i_y = 0, i_tile0 = 0, i_steps = 0, i_stage = 0;
+        const void *i_map = nullptr;
+        auto i_open = [&]() {
+            while (i_tile < tile_hi) {
+                if (i_tile >= i_tend) {
+                    TaProblem p;
+                    problem_at(i_pi, i_tend, i_tile, p);
+                    i_steps = ((p.K >> 8) - h + 1) >> 1;
+                    i_tile0 = p.tile0;
+                    i_map = nprob ? &maps[i_pi] : &single_map;
+                }
+                i_n = i_steps;
+                i_x = h * 128;
+                i_y = (i_tile - i_tile0) * kTileM + q * 32;     // rows past N read as zeros
+                i_j = 0;
+                if (i_n > 0) return;
+                ++i_tile;
             }
         };
         auto issue = [&]() {
-            if (is.tile < tile_hi) {
+            if (i_tile < tile_hi) {
                 if (lane == 0) {
                     const uint32_t bar = wbar(warp, i_stage);
                     mbar_expect_tx(bar, kWStage);
-                    tma_2d_g2s(wring + i_stage * kWStage, is.map, is.x, is.y, bar);
+                    tma_2d_g2s(wring + i_stage * kWStage, i_map, i_x, i_y, bar);
                 }
-                advance(is);
+                i_x += 256;
+                if (++i_j == i_n) { ++i_tile; i_open(); }
             }
             i_stage = (i_stage + 1 == kSW) ? 0 : i_stage + 1;
-            prefetch();
         };
-        open(pf);
-        open(is);
-        for (int s = 0; s < kSW + kL2Ahead; ++s) prefetch();
+        i_open();
 #pragma unroll
         for (int s = 0; s < kSW; ++s) issue();
 
-        // ---- consumer state
-        uint32_t wcount = 0;        // weight stages consumed so far
-        uint32_t t_h = 0;           // groups this half has handed to the MMA so far
-        uint32_t qcount = 0;        // quarter syncs so far
-        uint32_t t_fold = 0;        // groups folded into acc so far (t_fold <= t_h)
-        unsigned short raw_q[kRing] = {};   // fp16 scales (bits) of the groups in flight, by slot
-        float xsc[NB];              // 2^e of the batch rows (first half's threads, which write the outputs)
-        float acc[NB];
-        bool have_prev = false;     // a finished tile waiting for its last group and its output
-        TaProblem prev_p = single;
-        int prev_row = 0;
-
-        int c_pi = 0;
-        uint4 cb0 = make_uint4(0, 0, 0, 0), cb1 = cb0;     // this row's codebook (next tile's, once the tables are built)
+        // ---- per-row side data one tile ahead: GF4 codebook row
+        int f_pi = 0, f_tend = -1, f_tile0 = 0, f_N = 1;
+        const __half *f_cb = nullptr;
+        uint4 cb0 = make_uint4(0, 0, 0, 0), cb1 = cb0;
         auto fetch_codebook = [&](int tile) {
-            if (tile < tile_hi) {
-                int pi2 = c_pi;
-                const TaProblem p = problem_of(pi2, tile);
-                const int row = min((tile - p.tile0) * kTileM + r, p.N - 1);
-                const uint4 *src = reinterpret_cast<const uint4 *>(p.codebook + (size_t)row * 16);
+            if (kGf4 && tile < tile_hi) {
+                if (tile >= f_tend) {
+                    TaProblem p;
+                    problem_at(f_pi, f_tend, tile, p);
+                    f_tile0 = p.tile0; f_N = p.N; f_cb = p.codebook;
+                }
+                const int row = min((tile - f_tile0) * kTileM + r, f_N - 1);
+                const uint4 *src = reinterpret_cast<const uint4 *>(f_cb + (size_t)row * 16);
                 cb0 = __ldg(src);
                 cb1 = __ldg(src + 1);
             }
         };
+
+        // ---- consumer state
+        uint32_t wcount = 0;        // weight stages consumed so far
+        uint32_t t_h = 0;           // groups this half has handed to the MMA so far
+        uint32_t t_fold = 0;        // groups whose slot has been released (GF4: folded into acc) so far
+        uint32_t qcount = 0;        // quarter syncs so far
+        unsigned short raw_q[3] = {0, 0, 0};   // GF4: fp16 scales (bits) of the groups in flight, by slot
+        float acc[NB];
+        bool have_prev = false;     // a finished tile waiting for its last group and its outputs
+        float prev_bias = 0.f;
+        int prev_row = 0, prev_N = 0, prev_ldy = 0;
+        void *prev_y = nullptr;
+        float prev_xs[(NB + 31) / 32];   // lane l holds 2^e of batch rows l, l + 32 (loaded at the start of the tile)
+
         auto quarter_sync = [&]() -> bool {
             mbar_arrive(qbar(q));
             const bool ok = mbar_wait(qbar(q), qcount & 1, err);
             ++qcount;
             return ok;
         };
-        // fold the accumulator of group pend_t (scaled) into acc
-        auto fold_one = [&]() -> bool {   // the oldest group in flight
+        // release the oldest slot in flight: wait for its group's MMAs; GF4 folds the group's accumulator (scaled)
+        auto fold_one = [&]() -> bool {
             const uint32_t s = t_fold % kRing;
-            bool ok;
-            ok = __all_sync(0xffffffffu, mbar_wait(dbar(h, s), (t_fold / kRing) & 1, err));
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(dbar(h, s), (t_fold / kRing) & 1, err));
             if (!ok) return false;
-            tc_fence_after();
-            unsigned short raw = raw_q[0];
+            if constexpr (kGf4) {
+                tc_fence_after();
+                unsigned short raw = raw_q[0];
 #pragma unroll
-            for (int i = 1; i < kRing; ++i) raw = (s == (uint32_t)i) ? raw_q[i] : raw;
-            const float pend_scale = __half2float(__ushort_as_half(raw));
+                for (int i = 1; i < kRing; ++i) raw = (s == (uint32_t)i) ? raw_q[i] : raw;
+                const float sc = __half2float(__ushort_as_half(raw));
 #pragma unroll
-            for (int c = 0; c < NB; c += 16) {
-                uint32_t d[16];
-                tmem_ld16(lane_t + (h * kRing + s) * C::kRegion + 64 + c, d);
-                tmem_wait_ld();
+                for (int c = 0; c < NB; c += 16) {
+                    uint32_t d[16];
+                    tmem_ld16(lane_t + (h * kRing + s) * C::kSlot + 64 + c, d);
+                    tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 16; ++i) acc[c + i] = fmaf(__uint_as_float(d[i]), pend_scale, acc[c + i]);
+                    for (int i = 0; i < 16; ++i) acc[c + i] = fmaf(__uint_as_float(d[i]), sc, acc[c + i]);
+                }
             }
             ++t_fold;
             return true;
@@ -432,6 +440,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
             if (!have_prev) return true;
             while (t_fold < t_h)
                 if (!fold_one()) return false;
+            if constexpr (!kGf4) {          // the half's accumulator holds the whole row
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < NB; c += 16) {
+                    uint32_t d[16];
+                    tmem_ld16(lane_t + C::kAcc + h * NB + c, d);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) acc[c + i] = __uint_as_float(d[i]);
+                }
+            }
             if (h == 1) {
 #pragma unroll
                 for (int c = 0; c < NB; c += 16) {
@@ -441,13 +460,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
                     tmem_st16(lane_t + C::kExchange + c, v);
                 }
                 tmem_wait_st();
-                tc_fence_before();
             }
+            tc_fence_before();
             if (!quarter_sync()) return false;
             if (h == 0) {
                 tc_fence_after();
-                const bool live = prev_row < prev_p.N;
-                const float bias = (live && prev_p.bias) ? prev_p.bias[prev_row] : 0.f;
+                const bool live = prev_row < prev_N;
 #pragma unroll
                 for (int c = 0; c < NB; c += 16) {
                     uint32_t v[16];
@@ -456,11 +474,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const int b = c + i;
+                        const float xs_b = __shfl_sync(0xffffffffu, prev_xs[b >> 5], b & 31);
                         if (live && b < B) {
-                            const float o = fmaf(acc[b] + __uint_as_float(v[i]), xsc[b], bias);
+                            const float o = fmaf(acc[b] + __uint_as_float(v[i]), xs_b, prev_bias);
                             for (int cpy = 0; cpy < peers.n; ++cpy)
-                                jq::store_out(reinterpret_cast<char *>(prev_p.y) + peers.delta[cpy],
-                                              (size_t)b * prev_p.ldy + prev_row, o, y_dtype);
+                                jq::store_out(reinterpret_cast<char *>(prev_y) + peers.delta[cpy],
+                                              (size_t)b * prev_ldy + prev_row, o, y_dtype);
                         }
                     }
                 }
@@ -469,25 +488,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
             have_prev = false;
             return true;
         };
-        // 32 codes (four words) -> 16 fp16 pairs
-        auto lookup16 = [&](const uint4 &w4, uint32_t (&v)[16]) {
-#pragma unroll
-            for (int wi = 0; wi < 4; ++wi) {
-                const uint32_t w = wi == 0 ? w4.x : (wi == 1 ? w4.y : (wi == 2 ? w4.z : w4.w));
-#pragma unroll
-                for (int bj = 0; bj < 4; ++bj) v[wi * 4 + bj] = lds32(dp4a_u(w, 0x80u << (8 * bj), tcol));
-            }
-        };
 
+        int c_pi = 0, c_tend = -1;
+        TaProblem p = single;
         fetch_codebook(tile_lo);
         bool ok = true;
         for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
-            const TaProblem p = problem_of(c_pi, tile);
+            if (tile >= c_tend) problem_at(c_pi, c_tend, tile, p);
             const int row_raw = (tile - p.tile0) * kTileM + r;
             const int row = min(row_raw, p.N - 1);
-            // ---- the pair table of this row (this thread fills the entries whose second code is in its half)
-            if (!(ok = quarter_sync())) break;          // both warps are done with the previous tile's lookups
-            {
+            if constexpr (kGf4) {
+                // ---- the pair table of this row (this thread fills the entries whose second code is in its half)
+                if (!(ok = quarter_sync())) break;      // both warps are done with the previous tile's lookups
                 const uint32_t c[8] = {cb0.x, cb0.y, cb0.z, cb0.w, cb1.x, cb1.y, cb1.z, cb1.w};
                 uint32_t ch[4];
 #pragma unroll
@@ -501,21 +513,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
                                                        ((lo & 1) ? 0x32u : 0x10u) | (((i & 1) ? 0x76u : 0x54u) << 8));
                         asm volatile("st.shared.u32 [%0], %1;" ::"r"(tb + (i * 16 + lo) * 128), "r"(e) : "memory");
                     }
+                fetch_codebook(tile + 1);
             }
-            fetch_codebook(tile + 1);
-            // the previous tile's last group has had the table build to finish
+            // the previous tile's last groups have had the table build to finish; its sync also publishes the table
             const bool had_prev = have_prev;
-            if (!(ok = finish_prev())) break;           // (its quarter sync also publishes the new table)
-            if (!had_prev) { if (!(ok = quarter_sync())) break; }
+            if (!(ok = finish_prev())) break;
+            if (kGf4 && !had_prev) { if (!(ok = quarter_sync())) break; }
 #pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                acc[b] = 0.f;
-                if (h == 0) xsc[b] = b < B ? p.xscale[b] : 0.f;   // in flight during the tile, needed at its end
-            }
+            for (int b = 0; b < NB; ++b) acc[b] = 0.f;
 
+            float xs_next[(NB + 31) / 32];
+#pragma unroll
+            for (int i = 0; i < (NB + 31) / 32; ++i) xs_next[i] = (lane + 32 * i < B) ? p.xscale[lane + 32 * i] : 0.f;
             const int nsteps = ((p.K >> 8) - h + 1) >> 1;
             const unsigned short *srow = reinterpret_cast<const unsigned short *>(p.scales) + (size_t)row * p.lds;
-            const int gshift = 31 - __clz(p.g >> 7);   // log2 of the 128-code groups per scale (a power of two)
+            const int gshift = kGf4 ? 31 - __clz(p.g >> 7) : 0;   // GF4: log2 of the 128-code groups per scale
             for (int j = 0; j < nsteps && ok; ++j) {
                 const int stage = wcount % kSW;
                 ok = __all_sync(0xffffffffu, mbar_wait(wbar(warp, stage), (wcount / kSW) & 1, err));
@@ -526,22 +538,49 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
 #pragma unroll
                 for (int gi = 0; gi < 2; ++gi) {
                     const int grp = 2 * sg + gi;
-                    const unsigned short scale_raw = __ldg(srow + (grp >> gshift));
-                    // slot t % kRing is free once group t - kRing has been folded
-                    if (t_h - t_fold == kRing && !(ok = fold_one())) break;
+                    // this group's scales: GF4 one fp16 (per 128 * 2^k codes), E2M1 four (one per 32 codes)
+                    unsigned short scale_raw = 0;
+                    uint2 sc4 = make_uint2(0, 0);
+                    if constexpr (kGf4) scale_raw = __ldg(srow + (grp >> gshift));
+                    else sc4 = __ldg(reinterpret_cast<const uint2 *>(srow + grp * 4));
+                    // slot t % kRing is free once group t - kRing has been released
+                    if (t_h - t_fold == (uint32_t)kRing && !(ok = fold_one())) break;
                     const uint32_t t = t_h, s = t % kRing;
-                    const uint32_t a_t = lane_t + (h * kRing + s) * C::kRegion;
-                    // the lookups of the next 32 codes are issued before the previous 16 pairs are stored
+                    const uint32_t a_t = lane_t + (h * kRing + s) * C::kSlot;
                     uint4 w4[4];
 #pragma unroll
                     for (int part = 0; part < 4; ++part) w4[part] = lds128(slot + (((gi * 4 + part) << 4) ^ lkey));
+                    // 32 codes (four words) -> 16 fp16 pairs
+                    auto decode16 = [&](int part, uint32_t (&v)[16]) {
+#pragma unroll
+                        for (int wi = 0; wi < 4; ++wi) {
+                            const uint32_t w = wi == 0 ? w4[part].x : (wi == 1 ? w4[part].y : (wi == 2 ? w4[part].z : w4[part].w));
+                            if constexpr (kGf4) {
+#pragma unroll
+                                for (int bj = 0; bj < 4; ++bj) v[wi * 4 + bj] = lds32(dp4a_u(w, 0x80u << (8 * bj), tcol));
+                            } else {
+                                // E2M1: the group scale folded into the fp16 weight (one rounding per weight)
+                                const uint32_t sh = part == 0 ? (sc4.x & 0xffffu) : (part == 1 ? (sc4.x >> 16) : (part == 2 ? (sc4.y & 0xffffu) : (sc4.y >> 16)));
+                                const uint32_t s2 = sh * 0x00010001u;
+                                uint32_t hh[4];
+                                asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %4;\n"
+                                    "  cvt.rn.f16x2.e2m1x2 %0, b0; cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+                                    "  cvt.rn.f16x2.e2m1x2 %2, b2; cvt.rn.f16x2.e2m1x2 %3, b3; }"
+                                    : "=r"(hh[0]), "=r"(hh[1]), "=r"(hh[2]), "=r"(hh[3]) : "r"(w));
+#pragma unroll
+                                for (int bj = 0; bj < 4; ++bj)
+                                    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(v[wi * 4 + bj]) : "r"(hh[bj]), "r"(s2));
+                            }
+                        }
+                    };
+                    // the decode of the next 32 codes is issued before the previous 16 pairs are stored
                     uint32_t va[16], vb[16];
-                    lookup16(w4[0], va);
-                    lookup16(w4[1], vb);
+                    decode16(0, va);
+                    decode16(1, vb);
                     tmem_st16(a_t, va);
-                    lookup16(w4[2], va);
+                    decode16(2, va);
                     tmem_st16(a_t + 16, vb);
-                    lookup16(w4[3], vb);
+                    decode16(3, vb);
                     tmem_st16(a_t + 32, va);
                     tmem_st16(a_t + 48, vb);
                     tmem_wait_st();
@@ -557,64 +596,70 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
                 issue();                                // refill the stage just read
             }
             have_prev = true;
-            prev_p = p;
-            prev_row = row_raw;
+            prev_bias = (p.bias && row_raw < p.N) ? p.bias[row_raw] : 0.f;
+            prev_row = row_raw; prev_N = p.N; prev_ldy = p.ldy; prev_y = p.y;
+#pragma unroll
+            for (int i = 0; i < (NB + 31) / 32; ++i) prev_xs[i] = xs_next[i];
         }
         if (ok) ok = finish_prev();
-    } else if (warp == kDecodeWarps) {
-        // =============================== MMA issuer ===============================
+    } else if (warp == 8 || warp == 9) {
+        // =============================== MMA issuers, one per half ===============================
         if (lane == 0) {
+            const int h = warp - 8;
             constexpr uint32_t idesc = idesc_f16(kTileM, NB);
-            uint32_t tslot[2] = {0, 0}, tpar[2] = {0, 0};   // per half: slot of its next group, parity of that slot's phase
-            uint32_t xs = 0, xpar = 0;                      // activation stage in use and its phase parity
-            int pi = 0;
+            uint32_t slot = 0, par = 0;                 // A slot of this half's next group, parity of that slot's phase
+            uint32_t xstep = 0;                         // steps (of both halves) before the current tile
+            int pi = 0, t_end = -1, nsg = 0;
             bool ok = true;
             const uint32_t lbo = (uint32_t)B * 16;
             for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
-                const TaProblem p = problem_of(pi, tile);
-                const int ng = p.K >> 7;
-                int gin = 0;
-                uint32_t xb = sbase + S::kXRing + xs * xg.stage;
-                for (int g = 0; g < ng; ++g) {
-                    const int h = (g >> 1) & 1;
-                    const uint32_t s = tslot[h];
-                    if (gin == 0 && !(ok = mbar_wait(xbar(xs), xpar, err))) break;
-                    if (!(ok = mbar_wait(abar(h, s), tpar[h], err))) break;
-                    tc_fence_after();
-                    const uint32_t a_t = tmem + (h * kRing + s) * C::kRegion, d_t = a_t + 64;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        mma_f16_ts(d_t, a_t + 8 * i, smem_desc(xb + 2 * i * lbo, lbo, 128), idesc, i > 0);
-                    mma_commit(dbar(h, s));
-                    if (s + 1 == kRing) { tslot[h] = 0; tpar[h] ^= 1; } else tslot[h] = s + 1;
-                    xb += xg.chunk;
-                    if (++gin == xg.gps || g == ng - 1) {
-                        mma_commit(xebar(xs));          // the stage's chunks have been multiplied
-                        gin = 0;
-                        if (++xs == (uint32_t)xg.nstages) { xs = 0; xpar ^= 1; }
-                        xb = sbase + S::kXRing + xs * xg.stage;
-                    }
+                if (tile >= t_end) {
+                    TaProblem p;
+                    problem_at(pi, t_end, tile, p);
+                    nsg = p.K >> 8;
                 }
+                for (int sg = h; sg < nsg && ok; sg += 2) {
+                    const uint32_t u = xstep + sg, xs = u % xg.nstages, xpar = (u / xg.nstages) & 1;
+                    if (!(ok = mbar_wait(xbar(xs), xpar, err))) break;
+                    uint32_t xb = sbase + S::kXRing + xs * xg.stage;
+#pragma unroll
+                    for (int gi = 0; gi < 2; ++gi) {
+                        if (!(ok = mbar_wait(abar(h, slot), par, err))) break;
+                        tc_fence_after();
+                        const uint32_t a_t = tmem + (h * kRing + slot) * C::kSlot;
+                        const uint32_t d_t = kGf4 ? a_t + 64 : tmem + C::kAcc + h * NB;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            mma_f16_ts(d_t, a_t + 8 * i, smem_desc(xb + 2 * i * lbo, lbo, 128), idesc,
+                                       kGf4 ? (i > 0) : (i > 0 || gi > 0 || sg > h));
+                        mma_commit(dbar(h, slot));
+                        if (slot + 1 == (uint32_t)kRing) { slot = 0; par ^= 1; } else ++slot;
+                        xb += xg.chunk;
+                    }
+                    if (ok) mma_commit(xebar(xs));      // the step's activations have been multiplied
+                }
+                xstep += nsg;
             }
         }
-    } else {
+    } else if (warp == 10) {
         // =============================== activation producer ===============================
         if (lane == 0) {
-            uint32_t xc = 0;
-            int pi = 0;
+            uint32_t u = 0;
+            int pi = 0, t_end = -1, nsg = 0;
+            const unsigned char *xp = nullptr;
             bool ok = true;
             for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
-                const TaProblem p = problem_of(pi, tile);
-                const int ng = p.K >> 7;
-                for (int g0 = 0; g0 < ng; g0 += xg.gps, ++xc) {
-                    const int g1 = min(ng, g0 + xg.gps);
-                    const int xs = xc % xg.nstages;
-                    const uint32_t round = xc / xg.nstages;
+                if (tile >= t_end) {
+                    TaProblem p;
+                    problem_at(pi, t_end, tile, p);
+                    nsg = p.K >> 8;
+                    xp = reinterpret_cast<const unsigned char *>(p.xprep);
+                }
+                for (int sg = 0; sg < nsg; ++sg, ++u) {
+                    const uint32_t xs = u % xg.nstages, round = u / xg.nstages;
                     if (round > 0 && !(ok = mbar_wait(xebar(xs), (round - 1) & 1, err))) break;
-                    const uint32_t bytes = (uint32_t)(g1 - g0) * xg.chunk;
-                    mbar_expect_tx(xbar(xs), bytes);
-                    bulk_g2s(sbase + S::kXRing + xs * xg.stage,
-                             reinterpret_cast<const unsigned char *>(p.xprep) + (size_t)g0 * xg.chunk, bytes, xbar(xs));
+                    mbar_expect_tx(xbar(xs), xg.stage);
+                    bulk_g2s(sbase + S::kXRing + xs * xg.stage, xp + (size_t)sg * xg.stage, xg.stage, xbar(xs));
                 }
             }
         }
@@ -627,12 +672,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ta_gf4_kernel(const TaProble
     tc_fence_before();
     __syncthreads();
     if (tid == 0 && s_err) atomicExch(status, s_err);
-    if (warp == kDecodeWarps) {
+    if (warp == 11) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
     }
 }
-
 
 // ---- GF4, batch 1..2 on the CUDA cores ------------------------------------------------
 // Same tiles, same TMA weight ring, same per-row pair tables as the tensor-memory kernel above, but the
@@ -937,7 +981,12 @@ using namespace jqta;
 static const int kTaMagic = 0x4a515441;
 static const int kTaHeader = 12;
 
-static int ta_cols(int B) { return B <= 16 ? 16 : 0; }       // MMA N
+// MMA N: GF4 keeps one accumulator per group and slot (up to 16 columns); E2M1 one per half (up to 64)
+static int ta_cols(int fmt, int B) {
+    if (B <= 16) return 16;
+    if (fmt == JQ_FMT_E2M1) return B <= 32 ? 32 : (B <= 64 ? 64 : 0);
+    return 0;
+}
 
 static bool ta_use_lut(int B, int maxK);
 static size_t ta_align(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -983,16 +1032,16 @@ static bool ta_shape_ok(int fmt, int N, int K, int g, int had) {
         const int gq = g >> 7;
         return g >= 128 && g % 128 == 0 && (gq & (gq - 1)) == 0 && K % g == 0;
     }
-    return false;
+    return fmt == JQ_FMT_E2M1 && g == 32;
 }
 
 // batch 1..2 run on the CUDA cores when the prepared activation of one problem fits its shared-memory buffer
 static bool ta_use_lut(int B, int maxK) { return B <= 2 && (size_t)maxK * B * 2 <= (size_t)LutSmem::kXBytes; }
 
 extern "C" size_t jq_ta_workspace_bytes(const jq_problem *ph, int n, int B) {
-    if (!ph || n <= 0 || B < 1 || !ta_cols(B)) return 0;
+    if (!ph || n <= 0 || B < 1 || B > 64) return 0;
     size_t total = kHeaderBytes;
-    for (int i = 0; i < n; ++i) total += 128 + ta_align((size_t)ph[i].K * B * 2, 128);
+    for (int i = 0; i < n; ++i) total += 256 + ta_align((size_t)ph[i].K * B * 2, 128);
     return total;
 }
 
@@ -1007,7 +1056,7 @@ static int ta_fill_problem(TaProblem &t, int fmt, const jq_problem &p, unsigned 
     if (fmt == JQ_FMT_GF4 && !p.codebook) return JQ_ERR_NULL_PTR;
     if (!ta_shape_ok(fmt, p.N, p.K, p.g, p.had_block)) return JQ_ERR_UNSUPPORTED;
     if (!jq_aligned16(p.qweight) || (fmt == JQ_FMT_GF4 && !jq_aligned16(p.codebook)) ||
-        (reinterpret_cast<uintptr_t>(p.scales) & 1u))
+        (reinterpret_cast<uintptr_t>(p.scales) & (fmt == JQ_FMT_E2M1 ? 7u : 1u)))
         return JQ_ERR_BAD_ALIGN;
     t.qw = reinterpret_cast<const uint8_t *>(p.qweight);
     t.scales = reinterpret_cast<const __half *>(p.scales);
@@ -1016,7 +1065,7 @@ static int ta_fill_problem(TaProblem &t, int fmt, const jq_problem &p, unsigned 
     t.bias = p.bias;
     t.y = p.y;
     t.xscale = reinterpret_cast<float *>(ws + off);
-    off += 128;
+    off += 256;   // up to 64 batch rows
     t.xprep = reinterpret_cast<__half *>(ws + off);
     off += ta_align((size_t)p.K * B * 2, 128);
     t.N = p.N; t.K = p.K; t.g = p.g; t.had = p.had_block;
@@ -1031,7 +1080,7 @@ extern "C" int jq_ta_plan(int fmt, const jq_problem *ph, int n, int B, void *wor
                           void *plan_host, size_t plan_bytes) {
     if (!ph || !plan_host || !workspace_dev) return JQ_ERR_NULL_PTR;
     if (n <= 0 || B < 1) return JQ_ERR_BAD_SHAPE;
-    if (fmt != JQ_FMT_GF4 || !ta_cols(B)) return JQ_ERR_UNSUPPORTED;
+    if ((fmt != JQ_FMT_GF4 && fmt != JQ_FMT_E2M1) || !ta_cols(fmt, B)) return JQ_ERR_UNSUPPORTED;
     if (plan_bytes < jq_ta_plan_bytes(n) || workspace_bytes < jq_ta_workspace_bytes(ph, n, B)) return JQ_ERR_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(workspace_dev) & 127u) return JQ_ERR_BAD_ALIGN;
     const int grid = jq_sm_count();
@@ -1045,7 +1094,7 @@ extern "C" int jq_ta_plan(int fmt, const jq_problem *ph, int n, int B, void *wor
     double total = 0;
     int maxK = 0;
     for (int i = 0; i < n; ++i) maxK = ph[i].K > maxK ? ph[i].K : maxK;
-    const bool lut = ta_use_lut(B, maxK);
+    const bool lut = fmt == JQ_FMT_GF4 && ta_use_lut(B, maxK);
     const int tile_m = lut ? kLutTileM : kTileM;
     tile_start[0] = 0;
     for (int i = 0; i < n; ++i) {
@@ -1070,12 +1119,12 @@ extern "C" int jq_ta_plan(int fmt, const jq_problem *ph, int n, int B, void *wor
             acc += ph[i].K;
         }
     while (cta < grid) cta_first[++cta] = tile_start[n];
-    h[0] = kTaMagic; h[1] = n; h[2] = grid; h[3] = ta_cols(B); h[4] = (int)moff; h[5] = B; h[6] = fmt; h[7] = (int)poff;
+    h[0] = kTaMagic; h[1] = n; h[2] = grid; h[3] = ta_cols(fmt, B); h[4] = (int)moff; h[5] = B; h[6] = fmt; h[7] = (int)poff;
     h[8] = maxK; h[9] = h[10] = h[11] = 0;
     return JQ_OK;
 }
 
-template <int NB>
+template <int FMT, int NB>
 static int ta_launch(const TaProblem *probs_dev, const CUtensorMap *maps_dev, const TaProblem &single,
                      const CUtensorMap &single_map, int nprob, const int *tile_start,
                      const int *cta_first, int grid, int B, int x_dtype, int y_dtype, const jqta::PeerInfo &peers,
@@ -1084,12 +1133,12 @@ static int ta_launch(const TaProblem *probs_dev, const CUtensorMap *maps_dev, co
     ta_prepare_kernel<<<nblk, 256, 0, st>>>(probs_dev, single, B, x_dtype);
     int s = jq_launch_status();
     if (s) return s;
-    auto kern = gemm_ta_gf4_kernel<NB>;
-    constexpr int smem = Smem::kBytes;
+    auto kern = gemm_ta_kernel<FMT, NB>;
+    constexpr int smem = Smem<FMT>::kBytes;
     static_assert(smem <= 227 * 1024, "shared memory");
     JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<grid, kThreads, smem, st>>>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, B, y_dtype, peers,
-                                       status);
+    kern<<<grid, kTaThreads, smem, st>>>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, B, y_dtype, peers,
+                                         status);
     return jq_launch_status();
 }
 
@@ -1110,16 +1159,23 @@ static int lut2_launch(const TaProblem *probs_dev, const CUtensorMap *maps_dev, 
     return jq_launch_status();
 }
 
-static int ta_dispatch(int nb, int maxK, const TaProblem *probs_dev, const CUtensorMap *maps_dev, const TaProblem &single,
+static int ta_dispatch(int fmt, int nb, int maxK, const TaProblem *probs_dev, const CUtensorMap *maps_dev, const TaProblem &single,
                        const CUtensorMap &single_map, int nprob,
                        const int *tile_start, const int *cta_first, int grid, int B, int x_dtype, int y_dtype,
                        const jqta::PeerInfo &peers, int *status, cudaStream_t st) {
-    if (ta_use_lut(B, maxK)) {
-        if (B == 1) return lut2_launch<1>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, x_dtype, y_dtype, peers, status, st);
-        return lut2_launch<2>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, x_dtype, y_dtype, peers, status, st);
+#define JQ_TA_ARGS probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, B, x_dtype, y_dtype, peers, status, st
+    if (fmt == JQ_FMT_GF4) {
+        if (ta_use_lut(B, maxK)) {
+            if (B == 1) return lut2_launch<1>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, x_dtype, y_dtype, peers, status, st);
+            return lut2_launch<2>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, x_dtype, y_dtype, peers, status, st);
+        }
+        if (nb == 16) return ta_launch<JQ_FMT_GF4, 16>(JQ_TA_ARGS);
+        return JQ_ERR_UNSUPPORTED;
     }
-    if (nb == 16)
-        return ta_launch<16>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, B, x_dtype, y_dtype, peers, status, st);
+    if (nb == 16) return ta_launch<JQ_FMT_E2M1, 16>(JQ_TA_ARGS);
+    if (nb == 32) return ta_launch<JQ_FMT_E2M1, 32>(JQ_TA_ARGS);
+    if (nb == 64) return ta_launch<JQ_FMT_E2M1, 64>(JQ_TA_ARGS);
+#undef JQ_TA_ARGS
     return JQ_ERR_UNSUPPORTED;
 }
 
@@ -1140,7 +1196,7 @@ extern "C" int jq_gemm_ta_grouped(const void *plan_host, const void *plan_dev, v
     if (reinterpret_cast<uintptr_t>(maps) & 63u) return JQ_ERR_BAD_ALIGN;
     TaProblem none{};
     CUtensorMap nomap{};
-    return ta_dispatch(h[3], h[8], probs, maps, none, nomap, n, d + kTaHeader, d + kTaHeader + n + 1, grid, h[5], x_dtype, y_dtype,
+    return ta_dispatch(h[6], h[3], h[8], probs, maps, none, nomap, n, d + kTaHeader, d + kTaHeader + n + 1, grid, h[5], x_dtype, y_dtype,
                        peers, reinterpret_cast<int *>(workspace_dev), reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -1149,7 +1205,7 @@ extern "C" int jq_gemm_ta(int fmt, const void *qweight, const void *scales, cons
                           int y_dtype, void *workspace, size_t workspace_bytes, jq_stream_t stream) {
     if (!workspace) return JQ_ERR_NULL_PTR;
     if (B < 1) return JQ_ERR_BAD_SHAPE;
-    if (fmt != JQ_FMT_GF4 || !ta_cols(B)) return JQ_ERR_UNSUPPORTED;
+    if ((fmt != JQ_FMT_GF4 && fmt != JQ_FMT_E2M1) || !ta_cols(fmt, B)) return JQ_ERR_UNSUPPORTED;
     if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return JQ_ERR_BAD_DTYPE;
     if (reinterpret_cast<uintptr_t>(workspace) & 127u) return JQ_ERR_BAD_ALIGN;
     jq_problem p{};
@@ -1167,10 +1223,10 @@ extern "C" int jq_gemm_ta(int fmt, const void *qweight, const void *scales, cons
     peers.n = 1;
     for (int i = 0; i < 8; ++i) peers.delta[i] = 0;
     int grid = jq_sm_count();
-    const int tile_m = ta_use_lut(B, K) ? kLutTileM : kTileM;
+    const int tile_m = (fmt == JQ_FMT_GF4 && ta_use_lut(B, K)) ? kLutTileM : kTileM;
     const int tiles = (N + tile_m - 1) / tile_m;
     if (grid > tiles) grid = tiles;
-    return ta_dispatch(ta_cols(B), K, nullptr, nullptr, t, tm, 0, nullptr, nullptr, grid, B, x_dtype, y_dtype, peers,
+    return ta_dispatch(fmt, ta_cols(fmt, B), K, nullptr, nullptr, t, tm, 0, nullptr, nullptr, grid, B, x_dtype, y_dtype, peers,
                        reinterpret_cast<int *>(workspace), reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -1184,4 +1240,39 @@ extern "C" int jq_ta_status(void *workspace, int clear, jq_stream_t stream) {
     JQ_CUDA_TRY(cudaStreamSynchronize(st));
     if (clear && v) JQ_CUDA_TRY(cudaMemsetAsync(workspace, 0, sizeof(int), st));
     return v;
+}
+
+// ---- bounded-wait self test ------------------------------------------------------
+// One CTA waits, the way the pipelines above wait, on an mbarrier that nothing ever arrives on.  The wait
+// has to give up after the given number of polls, raise the status word and let the kernel return; the
+// device stays usable.  (This is how the failure path is exercised without faulting or hanging a GPU.)
+namespace jqta {
+__global__ void __launch_bounds__(64) bounded_wait_selftest_kernel(int *status, uint32_t limit) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int s_err;
+    if (threadIdx.x == 0) {
+        s_err = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    volatile int *err = &s_err;
+    if (threadIdx.x == 32) {          // one waiter; nobody arrives
+        bool ok = false;
+        for (uint32_t i = 0; i < limit; ++i) {
+            if (mbar_try(smem_u32(&bar), 0)) { ok = true; break; }
+            if (i > 64) __nanosleep(64);
+        }
+        if (!ok) *err = JQ_ERR_TIMEOUT;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *status = s_err;
+}
+}  // namespace jqta
+
+extern "C" int jq_selftest_bounded_wait(int *status_dev, unsigned int polls, jq_stream_t stream) {
+    if (!status_dev) return JQ_ERR_NULL_PTR;
+    if (polls == 0 || polls > (1u << 20)) return JQ_ERR_BAD_SHAPE;   // at most ~0.1 s of polling
+    jqta::bounded_wait_selftest_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status_dev, polls);
+    return jq_launch_status();
 }

@@ -1291,10 +1291,7 @@ static int dispatch_gemv(const GemvProblem &p, int B, int x_dtype, int y_dtype, 
     return JQ_OK;
 }
 
-size_t jq_tc_workspace_bytes(int N, int K, int B);  // gemm_tc.cu
-
 extern "C" size_t jq_workspace_bytes(int op, int N, int K, int B) {
-    if (op == JQ_OP_GEMM_TC) return jq_tc_workspace_bytes(N, K, B);
     if (op != JQ_OP_GEMV || N <= 0 || K <= 0 || B <= 0 || B > 8) return 0;
     if (gemv_fits_b<JQ_FMT_E2M1>(B, K) && gemv_fits_b<JQ_FMT_GF4>(B, K)) return 0;
     int tile = splitk_tile<JQ_FMT_E2M1>(B, K, 0);

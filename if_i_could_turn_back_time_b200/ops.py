@@ -18,9 +18,6 @@ from .spec import QuantSpec
 
 _DT = {torch.float32: _lib.JQ_F32, torch.float16: _lib.JQ_F16, torch.bfloat16: _lib.JQ_BF16}
 MAX_GEMV_BATCH = 8
-MAX_TC_BATCH = 64
-MAX_TA_BATCH = 16
-TC_MIN_BATCH = 17         # from here on E2M1 g32 goes to the tensor-core kernel (up to 16: two passes of the batch-8 loop are faster)
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -68,16 +65,23 @@ def fwht_block(x: torch.Tensor, block: int = 128) -> torch.Tensor:
 _OUT = {-1: None, _lib.JQ_F32: torch.float32, _lib.JQ_F16: torch.float16, _lib.JQ_BF16: torch.bfloat16}
 
 
-def tc_eligible(fmt_id: int, K: int, g: int, batch: int) -> bool:
-    return fmt_id == _lib.JQ_FMT_E2M1 and g == 32 and K % 256 == 0 and batch >= TC_MIN_BATCH
+def ta_max_batch(fmt_id: int) -> int:
+    """Rows one pass of the pair-table / tensor-memory kernels takes."""
+    return 16 if fmt_id == _lib.JQ_FMT_GF4 else 64
 
 
 def ta_eligible(fmt_id: int, K: int, g: int, batch: int) -> bool:
-    """GF4 problems the pair-table kernels take: batch 1..2 (CUDA-core loop) and
-    9..16 (tensor-memory kernel); in between the 16-bit-lookup MMA row loop is faster."""
-    gq = g >> 7
-    return (fmt_id == _lib.JQ_FMT_GF4 and g >= 128 and g % 128 == 0 and gq & (gq - 1) == 0 and K % g == 0
-            and K % 256 == 0 and K >= 512 and (batch <= 2 or 9 <= batch <= MAX_TA_BATCH))
+    """Problems the TMA-fed kernels take.  GF4 (group size 128 * 2^k): every
+    batch -- 1 (and 2 while the prepared activation fits in shared memory) on
+    the CUDA-core pair-table loop, the rest on the tensor-memory kernel, 16
+    rows per pass.  E2M1 g32: batches from 9 rows on the tensor-memory kernel,
+    64 rows per pass (up to 8 rows the mma.sync row loops are faster)."""
+    if K % 256 or K < 512:
+        return False
+    if fmt_id == _lib.JQ_FMT_GF4:
+        gq = g >> 7
+        return g >= 128 and g % 128 == 0 and gq & (gq - 1) == 0 and K % g == 0 and batch >= 1
+    return g == 32 and batch >= 9
 
 
 _ws_cache = {}
@@ -86,7 +90,7 @@ _checked = False
 
 def set_checked(on: bool) -> None:
     """Checked mode: every call that runs a kernel with device-side waits (the
-    tensor-core and tensor-memory kernels) is followed by a read of its status
+    pair-table and tensor-memory kernels) is followed by a read of its status
     word, which synchronises the stream, and raises if a wait gave up.  Off by
     default: the status stays in the workspace until ``check_status()``."""
     global _checked
@@ -96,8 +100,8 @@ def set_checked(on: bool) -> None:
 def _workspace(device, nbytes: int, kind: str = "gemv") -> torch.Tensor:
     """Grow-only scratch per (device, stream, kernel family): calls on one
     stream are ordered, so consecutive calls may share it; another stream gets
-    its own.  The families with a status word at offset 0 ("tc", "ta") never
-    share a buffer with the split-K partial sums, and start zeroed."""
+    its own.  The family with a status word at offset 0 ("ta") never shares
+    a buffer with the split-K partial sums, and starts zeroed."""
     key = (device, torch.cuda.current_stream(device).cuda_stream, kind)
     t = _ws_cache.get(key)
     if t is None or t.numel() < nbytes:
@@ -117,43 +121,19 @@ def check_status(raise_on_error: bool = True) -> int:
     dev = torch.device("cuda", torch.cuda.current_device())
     stream = torch.cuda.current_stream(dev).cuda_stream
     worst = 0
-    for kind in ("tc", "ta"):
-        ws = _ws_cache.get((dev, stream, kind))
-        if ws is None:
-            continue
-        st = lib.jq_tc_status(_ptr(ws), _stream()) if kind == "tc" else lib.jq_ta_status(_ptr(ws), 1, _stream())
-        worst = min(worst, st)
+    ws = _ws_cache.get((dev, stream, "ta"))
+    if ws is not None:
+        worst = min(worst, lib.jq_ta_status(_ptr(ws), 1, _stream()))
     if worst and raise_on_error:
         raise _lib.JqError(worst, "device status")
     return worst
 
 
-def tc_status() -> int:
-    """Status of the tensor-core kernel's calls on this stream since the last
-    read (synchronises, clears)."""
-    return check_status(raise_on_error=False)
-
-
-def _linear_rows_tc(x2, qweight, scales, bias, N, K, had, y):
+def _linear_rows_ta(x2, qweight, scales, codebook, bias, fmt_id, N, K, g, had, y):
+    """Through the TMA-fed kernels, at most ta_max_batch rows per pass."""
     lib = _lib.load()
     Bt = x2.shape[0]
-    with torch.cuda.device(x2.device):
-        for b0 in range(0, Bt, MAX_TC_BATCH):
-            b1 = min(Bt, b0 + MAX_TC_BATCH)
-            wsb = lib.jq_workspace_bytes(1, N, K, b1 - b0)
-            ws = _workspace(x2.device, wsb, "tc")
-            st = lib.jq_gemm_e2m1_tc(_ptr(qweight), _ptr(scales), _ptr(x2[b0:b1]), _ptr(bias), _ptr(y[b0:b1]), N, K,
-                                     b1 - b0, 32, had, _DT[x2.dtype], _DT[y.dtype], _ptr(ws), wsb, _stream())
-            _lib.check(st, "jq_gemm_e2m1_tc")
-    if _checked:
-        check_status()
-    return y
-
-
-def _linear_rows_ta(x2, qweight, scales, codebook, bias, N, K, g, had, y):
-    """GF4 through the pair-table kernels, at most MAX_TA_BATCH rows per pass."""
-    lib = _lib.load()
-    Bt = x2.shape[0]
+    MAX_TA_BATCH = ta_max_batch(fmt_id)
     prob = _lib.jq_problem()
     prob.K = K
     with _on(x2.device):
@@ -163,7 +143,7 @@ def _linear_rows_ta(x2, qweight, scales, codebook, bias, N, K, g, had, y):
             wsb = lib.jq_ta_workspace_bytes(ctypes.byref(prob), 1, b1 - b0)
             ws = _workspace(x2.device, wsb, "ta")
             xs, ys = (x2, y) if Bt <= MAX_TA_BATCH else (x2[b0:b1], y[b0:b1])
-            st = lib.jq_gemm_ta(_lib.JQ_FMT_GF4, _ptr(qweight), _ptr(scales), _ptr(codebook), _ptr(xs), _ptr(bias),
+            st = lib.jq_gemm_ta(fmt_id, _ptr(qweight), _ptr(scales), _ptr(codebook), _ptr(xs), _ptr(bias),
                                 _ptr(ys), N, K, b1 - b0, g, had, _DT[x2.dtype], _DT[y.dtype], _ptr(ws), ws.numel(), stream)
             _lib.check(st, "jq_gemm_ta")
     if _checked:
@@ -194,10 +174,8 @@ def _linear_rows(x2, qweight, scales, codebook, bias, fmt_id, N, K, g, had, out_
     lib = _lib.load()
     Bt = x2.shape[0]
     y = torch.empty((Bt, N), dtype=_OUT[out_id] or x2.dtype, device=x2.device)
-    if tc_eligible(fmt_id, K, g, Bt):
-        return _linear_rows_tc(x2, qweight, scales, bias, N, K, had, y)
-    if ta_eligible(fmt_id, K, g, min(Bt, MAX_TA_BATCH)) and (Bt <= 2 or Bt >= 9):
-        return _linear_rows_ta(x2, qweight, scales, codebook, bias, N, K, g, had, y)
+    if ta_eligible(fmt_id, K, g, Bt):
+        return _linear_rows_ta(x2, qweight, scales, codebook, bias, fmt_id, N, K, g, had, y)
     xd, yd = _DT[x2.dtype], _DT[y.dtype]
     qw_p, sc_p, cb_p, bias_p = _ptr(qweight), _ptr(scales), _ptr(codebook), _ptr(bias)
     with _on(x2.device):
@@ -341,16 +319,11 @@ class GroupedGemv:
         self._per_problem = False
         self._subs = []
         self._ta = []
-        self._use_tc = (self._symm is None and not any(self.row_offsets) and batch <= MAX_TC_BATCH
-                        and all(tc_eligible(w.spec.fmt_id, w.K, w.spec.group_size, batch) for w in weights))
-        if self._use_tc:
-            self.launches_per_run = None
-            return
-        self._ta = []
-        if (batch <= 2 or batch >= 9) and all(
-                ta_eligible(w.spec.fmt_id, w.K, w.spec.group_size, min(batch, 2)) for w in weights):
-            # GF4 through the pair-table kernels: one plan (and workspace) per sub-batch of at most 16 rows;
-            # a run is one activation-preparation launch plus one persistent launch per sub-batch
+        use_ta = all(ta_eligible(w.spec.fmt_id, w.K, w.spec.group_size, batch) for w in weights)
+        if use_ta:
+            MAX_TA_BATCH = ta_max_batch(spec0.fmt_id)
+            # through the TMA-fed kernels: one plan (and workspace) per sub-batch of at most 16 (GF4) or 64 (E2M1)
+            # rows; a run is one activation-preparation launch plus one persistent launch per sub-batch
             with torch.cuda.device(self.device):
                 for b0 in range(0, batch, MAX_TA_BATCH):
                     nb = min(MAX_TA_BATCH, batch - b0)
@@ -401,15 +374,13 @@ class GroupedGemv:
         lib = _lib.load()
         worst = 0
         with torch.cuda.device(self.device):
-            for _, _, ws in getattr(self, "_ta", []):
+            for _, _, ws in self._ta:
                 worst = min(worst, lib.jq_ta_status(_ptr(ws), 1 if clear else 0, _stream()))
-            if self._use_tc:
-                worst = min(worst, check_status(raise_on_error=False))
         return worst
 
     def run(self) -> None:
         lib = _lib.load()
-        if getattr(self, "_ta", None):
+        if self._ta:
             with torch.cuda.device(self.device):
                 for plan_host, plan_dev, ws in self._ta:
                     st = lib.jq_gemm_ta_grouped(plan_host.ctypes.data, _ptr(plan_dev), _ptr(ws), _DT[self.x_dtype],
@@ -417,7 +388,7 @@ class GroupedGemv:
                                                 _stream())
                     _lib.check(st, "jq_gemm_ta_grouped")
             return
-        if not self._per_problem and not self._use_tc:
+        if not self._per_problem:
             st = 0
             with torch.cuda.device(self.device):
                 for problems_dev, plan_host, plan_dev in self._subs:
@@ -433,17 +404,6 @@ class GroupedGemv:
                 _lib.check(st, "jq_gemv_grouped_peers")
             # batch x K too large for one staged activation per CTA: one (split-K) launch per matrix instead
             self._per_problem = True
-        if self._use_tc:
-            # every matrix goes to the tensor-core kernel: one host call enqueues them all
-            wsb = max(lib.jq_workspace_bytes(1, w.N, w.K, self.batch) for w in self.weights)
-            ws = _workspace(self.device, wsb, "tc")
-            with torch.cuda.device(self.device):
-                st = lib.jq_gemm_e2m1_tc_multi(ctypes.byref(self._problems_host), len(self.weights), self.batch,
-                                               _DT[self.x_dtype], _DT[self.x_dtype], _ptr(ws), ws.numel(), _stream())
-            _lib.check(st, "jq_gemm_e2m1_tc_multi")
-            if _checked:
-                check_status()
-            return
         for w, x, y, b, nf, ro in zip(self.weights, self.xs, self.ys, self.biases, self.full_rows, self.row_offsets):
             y[:, ro:ro + w.N].copy_(linear(x, w, b))
         self.launches_per_run = None

@@ -66,7 +66,6 @@ extern "C" {
 
 /* ops for jq_workspace_bytes */
 #define JQ_OP_GEMV 0
-#define JQ_OP_GEMM_TC 1
 #define JQ_OP_GROUPED 2
 
 typedef void *jq_stream_t;
@@ -144,36 +143,7 @@ int jq_gemv_noalloc(int fmt, const void *qweight, const void *scales_or_null,
                     void *y, int N, int K, int B, int g, int had_block, int x_dtype,
                     int y_dtype, jq_stream_t stream);
 
-/* Batched form on the tensor cores (tcgen05, kind::f8f6f4) for E2M1 weights
- * with g = 32 and 1 <= B <= 64 (meant for B >= 9; K % 256 == 0).  Replaces
- * the same F.linear(x, W_bar, bias) of Quantization_Experiments/layers.py:38
- * when the reference's evaluation loop feeds whole batches
- * (Python_Jenks_Test/Jenks_Tests/QuantNetworkTest.py:229-241, batch 128).
- * One K = 32 MMA per scale group into its own fp32 accumulator in tensor
- * memory; the fp16 group scale is applied by the epilogue in fp32.  The
- * activation is represented by a sum of E4M3 terms after a power-of-two
- * normalisation per batch row (2 terms for unrotated bf16 input = exact,
- * otherwise 3 terms = 12 significant bits).  workspace must hold
- * jq_workspace_bytes(JQ_OP_GEMM_TC, N, K, B) bytes (16-byte aligned); its
- * first word is a status (see jq_tc_status) and must be zero before the first
- * use of the workspace. */
-int jq_gemm_e2m1_tc(const void *qweight, const void *scales, const void *x,
-                    const float *bias_or_null, void *y, int N, int K, int B, int g,
-                    int had_block, int x_dtype, int y_dtype, void *workspace,
-                    size_t workspace_bytes, jq_stream_t stream);
-
-/* Status word of the jq_gemm_e2m1_tc calls on this workspace since it was
- * last read: 0, or JQ_ERR_TIMEOUT if a bounded device-side wait gave up in any
- * of them (that kernel returned early with y partly written; the device stays
- * usable).  The word is sticky: kernels only raise it, so a failure in one of
- * several launches that share the workspace is not overwritten by the next;
- * it must be zero before the workspace's first use, and this call clears it
- * after reading.  Synchronises the stream.  The reference's counterpart is the
- * blocking cudaDeviceSynchronize + launch check of
- * Python_Jenks_Test/Jenks_Tests/cuda_helpers.py:205-208. */
-int jq_tc_status(const void *workspace, jq_stream_t stream);
-
-/* Self test of the failure path of the pipeline's device-side waits: one CTA
+/* Self test of the failure path of the kernels' device-side waits: one CTA
  * polls (at most `polls` times, <= 2^20) an mbarrier that nothing arrives on,
  * gives up, and writes JQ_ERR_TIMEOUT to *status_dev (device int).  Nothing
  * traps or hangs; the context stays usable.  No reference counterpart (the
@@ -266,14 +236,6 @@ int jq_gemm_ta(int fmt, const void *qweight, const void *scales, const void *cod
                int had_block, int x_dtype, int y_dtype, void *workspace, size_t workspace_bytes,
                jq_stream_t stream);
 int jq_ta_status(void *workspace, int clear, jq_stream_t stream);
-
-/* n batched layers in one host call (problems_host is a HOST array whose
- * pointers are device pointers; ldy must be 0 or N): the launches are enqueued
- * back to back and share the workspace, which must be large enough for the
- * largest problem.  Same reference counterpart as jq_gemm_e2m1_tc. */
-int jq_gemm_e2m1_tc_multi(const jq_problem *problems_host, int n, int B, int x_dtype,
-                          int y_dtype, void *workspace, size_t workspace_bytes,
-                          jq_stream_t stream);
 
 /* Bytes of caller-provided device scratch an op needs for these sizes. */
 size_t jq_workspace_bytes(int op, int N, int K, int B);

@@ -112,6 +112,15 @@ def dequant_e2m1(codes: np.ndarray, scales: np.ndarray, g: int = 32) -> np.ndarr
     return (v.reshape(N, K // g, g) * s32[:, :, None]).astype(np.float32).reshape(N, K)
 
 
+def dequant_e2m1_folded_fp16(codes: np.ndarray, scales: np.ndarray, g: int = 32) -> np.ndarray:
+    """The weights the batched tensor-memory kernel multiplies by: the exact
+    product value(code) * scale (13 significant bits at most) rounded once to
+    fp16, because there the group scale is folded into the fp16 operand of the
+    tensor-core MMA instead of being applied in fp32 after the accumulation.
+    Used for the tight kernel check beside the 1e-3 gate against dequant_e2m1."""
+    return dequant_e2m1(codes, scales, g).astype(np.float16).astype(np.float32)
+
+
 # --------------------------------------------------------------------------
 # GF4 dequantise (the quantiser lives in oracle/jenks.py)
 # --------------------------------------------------------------------------
