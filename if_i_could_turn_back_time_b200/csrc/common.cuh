@@ -77,6 +77,21 @@ __device__ __forceinline__ void store_out(void *y, size_t i, float v, int dtype)
     else reinterpret_cast<__nv_bfloat16 *>(y)[i] = __float2bfloat16_rn(v);
 }
 
+// The same element of n <= 8 copies of the output (this rank's buffer and its peers'), copy c at byte offset
+// delta[c] from y.  The offset is picked with constant indices: indexing the array with a variable would make
+// the compiler keep it (and the structure around it) in local memory.
+template <class Delta>
+__device__ __forceinline__ long long peer_offset(const Delta &delta, int c) {
+    long long d = delta[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) d = (i == c) ? delta[i] : d;
+    return d;
+}
+template <class Delta>
+__device__ __forceinline__ void store_out_copies(void *y, const Delta &delta, int n, size_t i, float v, int dtype) {
+    for (int c = 0; c < n; ++c) store_out(reinterpret_cast<char *>(y) + peer_offset(delta, c), i, v, dtype);
+}
+
 // In-warp orthonormal Hadamard of one 128-block: lane holds elements
 // 4*lane .. 4*lane+3.  Stage order (strides 1,2,4,..,64) and the a+b / a-b
 // slot convention are part of the format contract: fp32 results must be

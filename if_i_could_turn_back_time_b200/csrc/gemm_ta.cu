@@ -41,9 +41,7 @@ constexpr int kDecodeWarps = 8;              // warps 0-3: first half of the ste
 constexpr int kTileM = 128;
 constexpr int kSW = 2;                       // stages of a decode warp's weight ring
 constexpr int kWStage = 32 * 128;            // bytes of a weight stage: 32 rows x 128 bytes (256 codes), swizzled by TMA
-constexpr int kXRingBytes = 24 * 1024;         // activation ring: stages of max(2 KB, one 128-code chunk)
-constexpr int kXMaxStages = 12;
-constexpr int kL2Ahead = 6;                  // steps by which the L2 prefetch runs ahead of the shared-memory fills
+constexpr int kXMaxStages = 8;               // stages of an MMA issuer's activation ring, at most
 constexpr int kTabBytes = 4 * 256 * 128;     // GF4: 256 entries x 32 lanes x 4 bytes per 32-row quarter
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr int kHeaderBytes = 1024;           // workspace: int status
@@ -234,10 +232,14 @@ constexpr int kTaThreads = 12 * 32;
 template <int FMT, int NB>
 struct Cols {
     static constexpr bool kGf4 = FMT == JQ_FMT_GF4;
-    static constexpr int kRing = (kGf4 || NB <= 32) ? 3 : 2;       // groups a half may have in flight
+    // MMA issuers per half.  One thread issues a tcgen05.mma every 50 clocks at best, whatever N up to 32 and
+    // whatever the accumulator; threads of different warps issue in parallel.  At N = 64 two issuers already
+    // saturate the pipe's arithmetic.
+    static constexpr int kIssuers = (!kGf4 && NB == 64) ? 1 : 2;
+    static constexpr int kRing = (kGf4 || NB <= 16) ? 3 : 2;       // groups a half may have in flight
     static constexpr int kSlot = 64 + (kGf4 ? NB : 0);
-    static constexpr int kAcc = 2 * kRing * kSlot;                 // E2M1: accumulator of half h at kAcc + h * NB
-    static constexpr int kExchange = kAcc + (kGf4 ? 0 : 2 * NB);
+    static constexpr int kAcc = 2 * kRing * kSlot;                 // E2M1: accumulator of (half h, issuer i) at kAcc + (h * kIssuers + i) * NB
+    static constexpr int kExchange = kAcc + (kGf4 ? 0 : 2 * kIssuers * NB);
     static_assert(kExchange + NB <= 512, "tensor memory");
 };
 
@@ -247,22 +249,30 @@ struct Smem {
     static constexpr int kTab = 0;
     static constexpr int kWRing = kGf4 ? kTabBytes : 0;
     static constexpr int kXRing = kWRing + kDecodeWarps * kSW * kWStage;
-    static constexpr int kXBytes = kGf4 ? 24 * 1024 : 144 * 1024;   // E2M1 has no tables: room for 64 batch rows per step
+    static constexpr int kXBytes = kGf4 ? 32 * 1024 : 144 * 1024;   // E2M1 has no tables: room for 64 batch rows per group
     static constexpr int kBars = kXRing + kXBytes + 512;            // + what the MMA reads past the last chunk (rows >= B)
-    static constexpr int kNumBars = kDecodeWarps * kSW + 4 * 3 + 2 * kXMaxStages + 4;   // weights, A full, MMAs done, x full/empty, quarter sync
+    static constexpr int kNumBars = kDecodeWarps * kSW + 4 * 3 + 2 * 4 * kXMaxStages + 4;   // weights, A full, MMAs done, x full/free per issuer, quarter sync
     static constexpr int kBytes = kBars + kNumBars * 8 + 1024;      // + slack for the 1 KB alignment of the base (TMA swizzle)
 };
 
-// geometry of the activation ring for a batch of B rows: a step (256 codes) is 512 B bytes
+// geometry of an issuer's activation ring for a batch of B rows: a stage is one group (128 codes), 256 B bytes
 struct XGeom {
-    int chunk, stage, nstages;
+    int chunk, ring, nstages, lag;
     __host__ __device__ XGeom(int B, int ring_bytes) {
         chunk = 256 * B;
-        stage = 2 * chunk;
-        nstages = ring_bytes / stage < kXMaxStages ? ring_bytes / stage : kXMaxStages;
+        ring = ring_bytes;
+        nstages = ring_bytes / chunk < kXMaxStages ? ring_bytes / chunk : kXMaxStages;
+        lag = nstages > 2 ? 2 : 1;      // a stage is refilled this many groups after the MMAs that read it were issued
     }
 };
 
+#ifdef JQ_TA_PROF
+#define PROF_BEGIN long long _pt = clock64();
+#define PROF_END(i) pc[i] += clock64() - _pt;
+#else
+#define PROF_BEGIN
+#define PROF_END(i)
+#endif
 template <int FMT, int NB>
 __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem *probs, const CUtensorMap *maps,
                                                                 const __grid_constant__ TaProblem single,
@@ -282,11 +292,11 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
     auto wbar = [&](int w, int s) { return bars + 8u * (w * kSW + s); };
     auto abar = [&](int h, int s) { return bars + 8u * (kDecodeWarps * kSW + h * 3 + s); };
     auto dbar = [&](int h, int s) { return bars + 8u * (kDecodeWarps * kSW + 6 + h * 3 + s); };
-    auto xbar = [&](int s) { return bars + 8u * (kDecodeWarps * kSW + 12 + s); };
-    auto xebar = [&](int s) { return bars + 8u * (kDecodeWarps * kSW + 12 + kXMaxStages + s); };
-    auto qbar = [&](int q) { return bars + 8u * (kDecodeWarps * kSW + 12 + 2 * kXMaxStages + q); };
+    auto xbar = [&](int iss, int s) { return bars + 8u * (kDecodeWarps * kSW + 12 + iss * kXMaxStages + s); };           // issuer's stage filled
+    auto xebar = [&](int iss, int s) { return bars + 8u * (kDecodeWarps * kSW + 12 + (4 + iss) * kXMaxStages + s); };    // its MMAs have read it
+    auto qbar = [&](int q) { return bars + 8u * (kDecodeWarps * kSW + 12 + 8 * kXMaxStages + q); };
     volatile int *err = &s_err;
-    const XGeom xg(B, S::kXBytes);
+    const XGeom xg(B, S::kXBytes / (2 * C::kIssuers));
 
     if (tid == 0) {
         s_err = 0;
@@ -297,7 +307,8 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                 mbar_init(abar(h, s), 128);                             // the 128 decode threads of the half
                 mbar_init(dbar(h, s), 1);                               // one tcgen05.commit
             }
-        for (int s = 0; s < kXMaxStages; ++s) { mbar_init(xbar(s), 1); mbar_init(xebar(s), 1); }
+        for (int i = 0; i < 4; ++i)
+            for (int s = 0; s < kXMaxStages; ++s) { mbar_init(xbar(i, s), 1); mbar_init(xebar(i, s), 1); }
         for (int q = 0; q < 4; ++q) mbar_init(qbar(q), 64);             // the two warps that share a quarter of the rows
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -329,6 +340,10 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
         t_end = tile_start[pi + 1];
     };
 
+#ifdef JQ_TA_PROF
+    long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long pt_start = clock64();
+#endif
     if (warp < kDecodeWarps) {
         // =============================== decode threads ===============================
         const int q = warp & 3, h = warp >> 2;
@@ -406,6 +421,15 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
         void *prev_y = nullptr;
         float prev_xs[(NB + 31) / 32];   // lane l holds 2^e of batch rows l, l + 32 (loaded at the start of the tile)
 
+        int pend_slot = -1;         // slot of the group whose tensor-memory stores are issued but not yet handed over
+        auto hand_over = [&]() {
+            if (pend_slot >= 0) {
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(abar(h, (uint32_t)pend_slot));
+                pend_slot = -1;
+            }
+        };
         auto quarter_sync = [&]() -> bool {
             mbar_arrive(qbar(q));
             const bool ok = mbar_wait(qbar(q), qcount & 1, err);
@@ -438,17 +462,22 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
         // outputs of the finished tile: the second half hands its sums over through tensor memory
         auto finish_prev = [&]() -> bool {
             if (!have_prev) return true;
+            { PROF_BEGIN
             while (t_fold < t_h)
                 if (!fold_one()) return false;
-            if constexpr (!kGf4) {          // the half's accumulator holds the whole row
+            PROF_END(6) }
+            if constexpr (!kGf4) {          // the accumulators of the half's issuers hold the whole row between them
                 tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < NB; c += 16) {
-                    uint32_t d[16];
-                    tmem_ld16(lane_t + C::kAcc + h * NB + c, d);
-                    tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) acc[c + i] = __uint_as_float(d[i]);
+                    for (int is = 0; is < C::kIssuers; ++is) {
+                        uint32_t d[16];
+                        tmem_ld16(lane_t + C::kAcc + (h * C::kIssuers + is) * NB + c, d);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) acc[c + i] = is ? acc[c + i] + __uint_as_float(d[i]) : __uint_as_float(d[i]);
+                    }
                 }
             }
             if (h == 1) {
@@ -462,8 +491,11 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                 tmem_wait_st();
             }
             tc_fence_before();
+            { PROF_BEGIN
             if (!quarter_sync()) return false;
+            PROF_END(7) }
             if (h == 0) {
+                PROF_BEGIN
                 tc_fence_after();
                 const bool live = prev_row < prev_N;
 #pragma unroll
@@ -475,18 +507,32 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                     for (int i = 0; i < 16; ++i) {
                         const int b = c + i;
                         const float xs_b = __shfl_sync(0xffffffffu, prev_xs[b >> 5], b & 31);
-                        if (live && b < B) {
-                            const float o = fmaf(acc[b] + __uint_as_float(v[i]), xs_b, prev_bias);
-                            for (int cpy = 0; cpy < peers.n; ++cpy)
-                                jq::store_out(reinterpret_cast<char *>(prev_y) + peers.delta[cpy],
-                                              (size_t)b * prev_ldy + prev_row, o, y_dtype);
-                        }
+                        acc[b] = fmaf(acc[b] + __uint_as_float(v[i]), xs_b, prev_bias);
                     }
                 }
+#ifndef JQ_TA_NOSTORE
+                if (live) {
+                    for (int cpy = 0; cpy < peers.n; ++cpy) {
+                        char *yb = reinterpret_cast<char *>(prev_y) + jq::peer_offset(peers.delta, cpy);
+#pragma unroll
+                        for (int b = 0; b < NB; ++b)
+                            if (b < B) jq::store_out(yb, (size_t)b * prev_ldy + prev_row, acc[b], y_dtype);
+                    }
+                }
+#endif
                 tc_fence_before();
+                PROF_END(4)
             }
             have_prev = false;
             return true;
+        };
+
+        // scales of one 256-code step of a row: E2M1 eight fp16 (16 bytes), GF4 one fp16 per 128 * 2^k codes (.x, .y)
+        auto load_scales = [&](const unsigned short *srow, int sg, int gshift) -> uint4 {
+            if constexpr (kGf4)
+                return make_uint4(__ldg(srow + ((2 * sg) >> gshift)), __ldg(srow + ((2 * sg + 1) >> gshift)), 0, 0);
+            else
+                return __ldg(reinterpret_cast<const uint4 *>(srow + sg * 8));
         };
 
         int c_pi = 0, c_tend = -1;
@@ -497,7 +543,12 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
             if (tile >= c_tend) problem_at(c_pi, c_tend, tile, p);
             const int row_raw = (tile - p.tile0) * kTileM + r;
             const int row = min(row_raw, p.N - 1);
+            const int nsteps = ((p.K >> 8) - h + 1) >> 1;
+            const unsigned short *srow = reinterpret_cast<const unsigned short *>(p.scales) + (size_t)row * p.lds;
+            const int gshift = kGf4 ? 31 - __clz(p.g >> 7) : 0;   // GF4: log2 of the 128-code groups per scale
+            uint4 sc_nxt = load_scales(srow, h, gshift);          // in flight during the table build / the previous tile's outputs
             if constexpr (kGf4) {
+                PROF_BEGIN
                 // ---- the pair table of this row (this thread fills the entries whose second code is in its half)
                 if (!(ok = quarter_sync())) break;      // both warps are done with the previous tile's lookups
                 const uint32_t c[8] = {cb0.x, cb0.y, cb0.z, cb0.w, cb1.x, cb1.y, cb1.z, cb1.w};
@@ -514,10 +565,13 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                         asm volatile("st.shared.u32 [%0], %1;" ::"r"(tb + (i * 16 + lo) * 128), "r"(e) : "memory");
                     }
                 fetch_codebook(tile + 1);
+                PROF_END(4)
             }
             // the previous tile's last groups have had the table build to finish; its sync also publishes the table
             const bool had_prev = have_prev;
+            { PROF_BEGIN
             if (!(ok = finish_prev())) break;
+            PROF_END(5) }
             if (kGf4 && !had_prev) { if (!(ok = quarter_sync())) break; }
 #pragma unroll
             for (int b = 0; b < NB; ++b) acc[b] = 0.f;
@@ -525,26 +579,26 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
             float xs_next[(NB + 31) / 32];
 #pragma unroll
             for (int i = 0; i < (NB + 31) / 32; ++i) xs_next[i] = (lane + 32 * i < B) ? p.xscale[lane + 32 * i] : 0.f;
-            const int nsteps = ((p.K >> 8) - h + 1) >> 1;
-            const unsigned short *srow = reinterpret_cast<const unsigned short *>(p.scales) + (size_t)row * p.lds;
-            const int gshift = kGf4 ? 31 - __clz(p.g >> 7) : 0;   // GF4: log2 of the 128-code groups per scale
             for (int j = 0; j < nsteps && ok; ++j) {
                 const int stage = wcount % kSW;
+                { PROF_BEGIN
                 ok = __all_sync(0xffffffffu, mbar_wait(wbar(warp, stage), (wcount / kSW) & 1, err));
+                PROF_END(1) }
                 if (!ok) break;
                 ++wcount;
                 const uint32_t slot = wring + stage * kWStage + lrow;
-                const int sg = 2 * j + h;
+                // the step's scales were loaded a step ahead; the next step's start their way now
+                const uint4 sc_cur = sc_nxt;
+                if (j + 1 < nsteps) sc_nxt = load_scales(srow, 2 * (j + 1) + h, gshift);
 #pragma unroll
                 for (int gi = 0; gi < 2; ++gi) {
-                    const int grp = 2 * sg + gi;
                     // this group's scales: GF4 one fp16 (per 128 * 2^k codes), E2M1 four (one per 32 codes)
-                    unsigned short scale_raw = 0;
-                    uint2 sc4 = make_uint2(0, 0);
-                    if constexpr (kGf4) scale_raw = __ldg(srow + (grp >> gshift));
-                    else sc4 = __ldg(reinterpret_cast<const uint2 *>(srow + grp * 4));
+                    const unsigned short scale_raw = (unsigned short)(gi ? sc_cur.y : sc_cur.x);
+                    const uint2 sc4 = gi ? make_uint2(sc_cur.z, sc_cur.w) : make_uint2(sc_cur.x, sc_cur.y);
                     // slot t % kRing is free once group t - kRing has been released
+                    { PROF_BEGIN
                     if (t_h - t_fold == (uint32_t)kRing && !(ok = fold_one())) break;
+                    PROF_END(2) }
                     const uint32_t t = t_h, s = t % kRing;
                     const uint32_t a_t = lane_t + (h * kRing + s) * C::kSlot;
                     uint4 w4[4];
@@ -573,19 +627,22 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                             }
                         }
                     };
-                    // the decode of the next 32 codes is issued before the previous 16 pairs are stored
+                    // the decode of the next 32 codes is issued before the previous 16 pairs are stored, and the
+                    // previous group is handed to the MMA issuer only once this group's first lookups are under way
+                    // (its tensor-memory stores have had that long to land)
                     uint32_t va[16], vb[16];
                     decode16(0, va);
                     decode16(1, vb);
+                    { PROF_BEGIN
+                    hand_over();
+                    PROF_END(3) }
                     tmem_st16(a_t, va);
                     decode16(2, va);
                     tmem_st16(a_t + 16, vb);
                     decode16(3, vb);
                     tmem_st16(a_t + 32, va);
                     tmem_st16(a_t + 48, vb);
-                    tmem_wait_st();
-                    tc_fence_before();
-                    mbar_arrive(abar(h, s));
+                    pend_slot = (int)s;
                     ++t_h;
 #pragma unroll
                     for (int i = 0; i < kRing; ++i) raw_q[i] = (s == (uint32_t)i) ? scale_raw : raw_q[i];
@@ -595,6 +652,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                 fence_async_smem();
                 issue();                                // refill the stage just read
             }
+            hand_over();
             have_prev = true;
             prev_bias = (p.bias && row_raw < p.N) ? p.bias[row_raw] : 0.f;
             prev_row = row_raw; prev_N = p.N; prev_ldy = p.ldy; prev_y = p.y;
@@ -602,66 +660,97 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
             for (int i = 0; i < (NB + 31) / 32; ++i) prev_xs[i] = xs_next[i];
         }
         if (ok) ok = finish_prev();
-    } else if (warp == 8 || warp == 9) {
-        // =============================== MMA issuers, one per half ===============================
-        if (lane == 0) {
-            const int h = warp - 8;
-            constexpr uint32_t idesc = idesc_f16(kTileM, NB);
-            uint32_t slot = 0, par = 0;                 // A slot of this half's next group, parity of that slot's phase
-            uint32_t xstep = 0;                         // steps (of both halves) before the current tile
-            int pi = 0, t_end = -1, nsg = 0;
-            bool ok = true;
-            const uint32_t lbo = (uint32_t)B * 16;
-            for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
-                if (tile >= t_end) {
-                    TaProblem p;
-                    problem_at(pi, t_end, tile, p);
-                    nsg = p.K >> 8;
-                }
-                for (int sg = h; sg < nsg && ok; sg += 2) {
-                    const uint32_t u = xstep + sg, xs = u % xg.nstages, xpar = (u / xg.nstages) & 1;
-                    if (!(ok = mbar_wait(xbar(xs), xpar, err))) break;
-                    uint32_t xb = sbase + S::kXRing + xs * xg.stage;
-#pragma unroll
-                    for (int gi = 0; gi < 2; ++gi) {
-                        if (!(ok = mbar_wait(abar(h, slot), par, err))) break;
-                        tc_fence_after();
-                        const uint32_t a_t = tmem + (h * kRing + slot) * C::kSlot;
-                        const uint32_t d_t = kGf4 ? a_t + 64 : tmem + C::kAcc + h * NB;
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            mma_f16_ts(d_t, a_t + 8 * i, smem_desc(xb + 2 * i * lbo, lbo, 128), idesc,
-                                       kGf4 ? (i > 0) : (i > 0 || gi > 0 || sg > h));
-                        mma_commit(dbar(h, slot));
-                        if (slot + 1 == (uint32_t)kRing) { slot = 0; par ^= 1; } else ++slot;
-                        xb += xg.chunk;
-                    }
-                    if (ok) mma_commit(xebar(xs));      // the step's activations have been multiplied
-                }
-                xstep += nsg;
-            }
+#ifdef JQ_TA_PROF
+        if (blockIdx.x == 0 && q == 0 && lane == 0) {
+            long long *pr = reinterpret_cast<long long *>(status) + 8 + h * 8;
+            pc[0] = clock64() - pt_start;
+            for (int i = 0; i < 8; ++i) pr[i] = pc[i];
         }
-    } else if (warp == 10) {
-        // =============================== activation producer ===============================
-        if (lane == 0) {
-            uint32_t u = 0;
-            int pi = 0, t_end = -1, nsg = 0;
-            const unsigned char *xp = nullptr;
+#endif
+    } else {
+        // =============================== MMA issuers ===============================
+        // Warps 8, 9: half 0, 1; warps 10, 11: a second issuer per half (kIssuers == 2).  With two issuers a half's
+        // groups alternate between them (the first group of every 256-code step to one, the second to the other).
+        // Every issuer owns a ring of activation stages (one 128-code group each) that it fills itself, so the
+        // only thing it ever waits for besides the decode threads is its own earlier work.
+        const int h = (warp - 8) & 1, sub = (warp - 8) >> 1, iss = warp - 8;
+        if (lane == 0 && sub < C::kIssuers) {
+            constexpr uint32_t idesc = idesc_f16(kTileM, NB);
+            constexpr int kPer = 2 / C::kIssuers;       // groups of a step this issuer takes
+            const uint32_t lbo = (uint32_t)B * 16;
+            const uint32_t ring = sbase + S::kXRing + iss * xg.ring;
+            // two walks over the same sequence of groups: the loads run ahead of the MMAs
+            struct Walk { int tile, pi, t_end, nsg, sg, k; const unsigned char *xp; };
+            auto open_tile = [&](Walk &w) {
+                while (w.tile < tile_hi) {
+                    if (w.tile >= w.t_end) {
+                        TaProblem p;
+                        problem_at(w.pi, w.t_end, w.tile, p);
+                        w.nsg = p.K >> 8;
+                        w.xp = reinterpret_cast<const unsigned char *>(p.xprep);
+                    }
+                    w.sg = h; w.k = 0;
+                    if (w.sg < w.nsg) return;
+                    ++w.tile;
+                }
+            };
+            auto advance = [&](Walk &w) {
+                if (++w.k == kPer) { w.k = 0; w.sg += 2; }
+                if (w.sg >= w.nsg) { ++w.tile; open_tile(w); }
+            };
+            Walk ld = {tile_lo, 0, -1, 0, 0, 0, nullptr};
+            open_tile(ld);
+            Walk mm = ld;
+            uint32_t n_ld = 0;
+            auto load_next = [&]() {
+                if (ld.tile < tile_hi) {
+                    const uint32_t s = n_ld % xg.nstages;
+                    const int G = 2 * ld.sg + (C::kIssuers == 2 ? sub : ld.k);
+                    mbar_expect_tx(xbar(iss, s), xg.chunk);
+                    bulk_g2s(ring + s * xg.chunk, ld.xp + (size_t)G * xg.chunk, xg.chunk, xbar(iss, s));
+                    advance(ld);
+                }
+                ++n_ld;
+            };
+            for (int i = 0; i < xg.nstages; ++i) load_next();
             bool ok = true;
-            for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
-                if (tile >= t_end) {
-                    TaProblem p;
-                    problem_at(pi, t_end, tile, p);
-                    nsg = p.K >> 8;
-                    xp = reinterpret_cast<const unsigned char *>(p.xprep);
+            for (uint32_t n = 0; mm.tile < tile_hi && ok; ++n) {
+                // the stage whose MMAs were issued xg.lag groups ago is free by now: refill it
+                if (n >= (uint32_t)xg.lag) {
+                    const uint32_t m = n - xg.lag;
+                    if (!(ok = mbar_wait(xebar(iss, m % xg.nstages), (m / xg.nstages) & 1, err))) break;
+                    load_next();
                 }
-                for (int sg = 0; sg < nsg; ++sg, ++u) {
-                    const uint32_t xs = u % xg.nstages, round = u / xg.nstages;
-                    if (round > 0 && !(ok = mbar_wait(xebar(xs), (round - 1) & 1, err))) break;
-                    mbar_expect_tx(xbar(xs), xg.stage);
-                    bulk_g2s(sbase + S::kXRing + xs * xg.stage, xp + (size_t)sg * xg.stage, xg.stage, xbar(xs));
-                }
+                const uint32_t s = n % xg.nstages;
+                { PROF_BEGIN
+                if (!(ok = mbar_wait(xbar(iss, s), (n / xg.nstages) & 1, err))) break;
+                PROF_END(1) }
+                const uint32_t t = C::kIssuers == 2 ? 2 * n + sub : n;     // the half's group count
+                const uint32_t slot = t % kRing, par = (t / kRing) & 1;
+                { PROF_BEGIN
+                if (!(ok = mbar_wait(abar(h, slot), par, err))) break;
+                PROF_END(2) }
+                tc_fence_after();
+                const uint32_t a_t = tmem + (h * kRing + slot) * C::kSlot;
+                const uint32_t d_t = kGf4 ? a_t + 64 : tmem + C::kAcc + (h * C::kIssuers + sub) * NB;
+                const uint32_t xb = ring + s * xg.chunk;
+                const bool first = mm.sg == h && mm.k == 0;                // E2M1: this issuer's first group of the tile
+                { PROF_BEGIN
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    mma_f16_ts(d_t, a_t + 8 * i, smem_desc(xb + 2 * i * lbo, lbo, 128), idesc, kGf4 ? (i > 0) : (i > 0 || !first));
+                mma_commit(dbar(h, slot));
+                mma_commit(xebar(iss, s));
+                PROF_END(3) }
+                advance(mm);
             }
+#ifdef JQ_TA_PROF
+            if (blockIdx.x == 0) {
+                long long *pr = reinterpret_cast<long long *>(status) + 8 + 16 + iss * 8;
+                pc[0] = clock64() - pt_start;
+                for (int i = 0; i < 8; ++i) pr[i] = pc[i];
+            }
+#endif
         }
     }
 
@@ -844,8 +933,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
 #pragma unroll
                 for (int hh = 1; hh < kLutSplit; ++hh) v += ps[((hh - 1) * kLutTileM + r) * 2 + b];
                 const float o = fmaf(v, prev_xsc[b], prev_bias);
-                for (int cpy = 0; cpy < peers.n; ++cpy)
-                    jq::store_out(reinterpret_cast<char *>(prev_y) + peers.delta[cpy], (size_t)b * prev_ldy + prev_row, o, y_dtype);
+                jq::store_out_copies(prev_y, peers.delta, peers.n, (size_t)b * prev_ldy + prev_row, o, y_dtype);
             }
         }
         have_prev = false;
@@ -1056,7 +1144,7 @@ static int ta_fill_problem(TaProblem &t, int fmt, const jq_problem &p, unsigned 
     if (fmt == JQ_FMT_GF4 && !p.codebook) return JQ_ERR_NULL_PTR;
     if (!ta_shape_ok(fmt, p.N, p.K, p.g, p.had_block)) return JQ_ERR_UNSUPPORTED;
     if (!jq_aligned16(p.qweight) || (fmt == JQ_FMT_GF4 && !jq_aligned16(p.codebook)) ||
-        (reinterpret_cast<uintptr_t>(p.scales) & (fmt == JQ_FMT_E2M1 ? 7u : 1u)))
+        (reinterpret_cast<uintptr_t>(p.scales) & (fmt == JQ_FMT_E2M1 ? 15u : 1u)))
         return JQ_ERR_BAD_ALIGN;
     t.qw = reinterpret_cast<const uint8_t *>(p.qweight);
     t.scales = reinterpret_cast<const __half *>(p.scales);

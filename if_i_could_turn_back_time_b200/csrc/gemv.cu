@@ -272,7 +272,10 @@ __device__ __forceinline__ void finish_rows(const GemvProblem &p, int crg, float
         const int row = crg * T + r_l;
         if (c_l < p.npeer && row < N) {
             const float bias = p.bias ? p.bias[row] : 0.f;
-            void *yc = reinterpret_cast<char *>(p.y) + p.peer_delta[c_l];
+            long long delta = 0;     // selected with constant indices: a variable index would put the problem in local memory
+#pragma unroll
+            for (int c = 0; c < 8; ++c) delta = (c == c_l) ? p.peer_delta[c] : delta;
+            void *yc = reinterpret_cast<char *>(p.y) + delta;
 #pragma unroll
             for (int b = 0; b < B; ++b) {
                 float v = 0.f;
@@ -705,8 +708,7 @@ __device__ __forceinline__ void mma_task_end(const GemvProblem &p, float (&acc)[
                     if (b < B) {
                         const float up = __uint_as_float((uint32_t)(127 + sexp[b]) << 23);  // 2^e
                         const float v = fmaf(acc[2 * h + j], up, bias);
-                        for (int cpy = 0; cpy < p.npeer; ++cpy)
-                            store_out(reinterpret_cast<char *>(p.y) + p.peer_delta[cpy], (size_t)b * p.ldy + row, v, y_dtype);
+                        store_out_copies(p.y, p.peer_delta, p.npeer, (size_t)b * p.ldy + row, v, y_dtype);
                     }
                 }
             }
@@ -1073,8 +1075,7 @@ __device__ void rows_k_tiled(const GemvProblem &p, int rg_lo, int rg_hi, const S
             if (row < p.N) {
                 const float up = __uint_as_float((uint32_t)(127 + L.sexp[b]) << 23);  // 2^e
                 const float v = fmaf(partial[i], up, p.bias ? p.bias[row] : 0.f);
-                for (int cpy = 0; cpy < p.npeer; ++cpy)
-                    store_out(reinterpret_cast<char *>(p.y) + p.peer_delta[cpy], (size_t)b * p.ldy + row, v, y_dtype);
+                store_out_copies(p.y, p.peer_delta, p.npeer, (size_t)b * p.ldy + row, v, y_dtype);
             }
         }
     }
