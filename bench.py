@@ -516,7 +516,7 @@ def main():
         achieved = alg / (k_ms * 1e-3) / 1e9
         if grp._ta:
             max_k = max(w.K for w in grp.weights)
-            lut = grp.weights[0].spec.fmt == "gf4" and args.batch <= 2 and max_k * args.batch * 2 <= 24 * 1024
+            lut = grp.weights[0].spec.fmt == "gf4" and args.batch == 1 and max_k * 2 <= 24 * 1024
             kernel = ("gf4_lut2_kernel" if lut else "gemm_ta_kernel<%s>" % grp.weights[0].spec.fmt) + " (+ ta_prepare_kernel)"
         else:
             kernel = "gemv_grouped_kernel"

@@ -7,7 +7,7 @@
 //   * the packed codes of a warp's 32 rows arrive by TMA (cp.async.bulk.tensor,
 //     one 32-row x 128-byte box per step with the 128-byte swizzle, completion
 //     counted on an mbarrier), so that every lane reads its own row without
-//     bank conflicts; later steps are prefetched into L2 by the same engine;
+//     bank conflicts;
 //   * GF4: a byte (two codes) indexes the row's 256-entry table of fp16 pairs,
 //     built once per tile in a shared-memory column that only this lane's bank
 //     serves (one conflict-free 32-bit lookup per two codes, the address formed
@@ -16,14 +16,15 @@
 //   * the fp16 values go to tensor memory with tcgen05.st as the A operand
 //     (M = 128 rows, K = 16 per instruction) of tcgen05.mma kind::f16; the B
 //     operand is the prepared activation (rotated, normalised by a power of
-//     two, fp16, in the K-major core-matrix layout) that a producer thread
-//     streams from global memory, one 128-code chunk per bulk copy;
+//     two, fp16, in the K-major core-matrix layout) that each MMA-issuing
+//     thread streams from global memory into a ring of its own, one 128-code
+//     chunk per bulk copy;
 //   * GF4 keeps one fp32 accumulator per 128-code scale group in tensor memory;
 //     the thread reads its row's sums back with tcgen05.ld and applies the
 //     group's fp16 scale in fp32, so every product and every scale stays exact
 //     (the results differ from the FMA kernels only in summation order).
 //     E2M1 folds the scale into the fp16 weight (one rounding per weight) and
-//     accumulates the whole row in one accumulator.
+//     accumulates the whole row in one accumulator per issuing thread.
 // The multiply-accumulate work thus costs the CUDA cores nothing, whatever the
 // batch (up to 64 columns per pass), and the lookups are halved.
 //
@@ -39,7 +40,6 @@ namespace jqta {
 
 constexpr int kDecodeWarps = 8;              // warps 0-3: first half of the steps, warps 4-7: second half
 constexpr int kTileM = 128;
-constexpr int kSW = 2;                       // stages of a decode warp's weight ring
 constexpr int kWStage = 32 * 128;            // bytes of a weight stage: 32 rows x 128 bytes (256 codes), swizzled by TMA
 constexpr int kXMaxStages = 8;               // stages of an MMA issuer's activation ring, at most
 constexpr int kTabBytes = 4 * 256 * 128;     // GF4: 256 entries x 32 lanes x 4 bytes per 32-row quarter
@@ -219,15 +219,23 @@ __global__ void __launch_bounds__(256) ta_prepare_kernel(const TaProblem *probs,
 
 // ---- main kernel --------------------------------------------------------------------
 // Roles of a CTA (12 warps): warps 0-7 decode (warp = 32-row quarter q of the tile x half h of the 256-code
-// steps of a row: step sg belongs to half sg & 1), warps 8 and 9 each issue the MMAs of one half (lane 0),
-// warp 10 streams the prepared activation (lane 0), warp 11 owns the tensor-memory allocation.  The two
-// halves are independent pipelines that share only the tensor pipe and the activation ring.
+// steps of a row: step sg belongs to half sg & 1); lane 0 of warps 8-11 issues MMAs (two issuers per half:
+// a thread cannot issue a tcgen05.mma more often than every 50 clocks, threads of different warps can) and
+// streams the prepared activation of its own groups; warp 11 also owns the tensor-memory allocation.  The
+// two halves are independent pipelines that meet at the end of a tile.
 //
 // Tensor-memory columns: kRing slots per half of 64 columns each for the A operand (one 128-code group);
 // GF4 adds NB accumulator columns to every slot (one accumulator per group: the group's fp16 scale is
-// applied in fp32 after tcgen05.ld), E2M1 has one accumulator of NB columns per half for the whole row
+// applied in fp32 after tcgen05.ld), E2M1 has one accumulator of NB columns per issuer for the whole row
 // (its scales are folded into the fp16 weights).  NB more columns carry the second half's sums to the
 // first half's threads at the end of a tile.
+//
+// Where the time goes (clock64 counters per role, 11008 x 4096 GF4 and 8192 x 8192 E2M1, 16 batch rows): the
+// decode threads are busy decoding for about 60 % of a tile (GF4: the shared-memory pipe, 80 wavefronts per
+// 128 codes of 32 rows, is 3/4 full while they do; E2M1: about 230 instructions per 128 codes and thread),
+// the rest goes to the table build, the accumulator read-back and the end of the tile; the MMA issuers are
+// idle most of the time and neither the weight ring nor the activation rings are waited for (deepening the
+// weight ring to four stages changed nothing).  With the MMAs left out E2M1 runs 17 % faster, GF4 7 %.
 constexpr int kTaThreads = 12 * 32;
 template <int FMT, int NB>
 struct Cols {
@@ -248,10 +256,11 @@ struct Smem {
     static constexpr bool kGf4 = FMT == JQ_FMT_GF4;
     static constexpr int kTab = 0;
     static constexpr int kWRing = kGf4 ? kTabBytes : 0;
+    static constexpr int kSW = 2;       // stages of a decode warp's weight ring (four did not change anything: the ring is not what the decode threads wait for)
     static constexpr int kXRing = kWRing + kDecodeWarps * kSW * kWStage;
     static constexpr int kXBytes = kGf4 ? 32 * 1024 : 144 * 1024;   // E2M1 has no tables: room for 64 batch rows per group
     static constexpr int kBars = kXRing + kXBytes + 512;            // + what the MMA reads past the last chunk (rows >= B)
-    static constexpr int kNumBars = kDecodeWarps * kSW + 4 * 3 + 2 * 4 * kXMaxStages + 4;   // weights, A full, MMAs done, x full/free per issuer, quarter sync
+    static constexpr int kNumBars = kDecodeWarps * 4 + 4 * 3 + 2 * 4 * kXMaxStages + 4;   // weights, A full, MMAs done, x full/free per issuer, quarter sync
     static constexpr int kBytes = kBars + kNumBars * 8 + 1024;      // + slack for the 1 KB alignment of the base (TMA swizzle)
 };
 
@@ -266,13 +275,6 @@ struct XGeom {
     }
 };
 
-#ifdef JQ_TA_PROF
-#define PROF_BEGIN long long _pt = clock64();
-#define PROF_END(i) pc[i] += clock64() - _pt;
-#else
-#define PROF_BEGIN
-#define PROF_END(i)
-#endif
 template <int FMT, int NB>
 __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem *probs, const CUtensorMap *maps,
                                                                 const __grid_constant__ TaProblem single,
@@ -283,6 +285,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
     using S = Smem<FMT>;
     constexpr bool kGf4 = FMT == JQ_FMT_GF4;
     constexpr int kRing = C::kRing;
+    constexpr int kSW = S::kSW;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
@@ -340,10 +343,6 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
         t_end = tile_start[pi + 1];
     };
 
-#ifdef JQ_TA_PROF
-    long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const long long pt_start = clock64();
-#endif
     if (warp < kDecodeWarps) {
         // =============================== decode threads ===============================
         const int q = warp & 3, h = warp >> 2;
@@ -462,10 +461,8 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
         // outputs of the finished tile: the second half hands its sums over through tensor memory
         auto finish_prev = [&]() -> bool {
             if (!have_prev) return true;
-            { PROF_BEGIN
             while (t_fold < t_h)
                 if (!fold_one()) return false;
-            PROF_END(6) }
             if constexpr (!kGf4) {          // the accumulators of the half's issuers hold the whole row between them
                 tc_fence_after();
 #pragma unroll
@@ -491,11 +488,8 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                 tmem_wait_st();
             }
             tc_fence_before();
-            { PROF_BEGIN
             if (!quarter_sync()) return false;
-            PROF_END(7) }
             if (h == 0) {
-                PROF_BEGIN
                 tc_fence_after();
                 const bool live = prev_row < prev_N;
 #pragma unroll
@@ -510,7 +504,6 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                         acc[b] = fmaf(acc[b] + __uint_as_float(v[i]), xs_b, prev_bias);
                     }
                 }
-#ifndef JQ_TA_NOSTORE
                 if (live) {
                     for (int cpy = 0; cpy < peers.n; ++cpy) {
                         char *yb = reinterpret_cast<char *>(prev_y) + jq::peer_offset(peers.delta, cpy);
@@ -519,9 +512,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                             if (b < B) jq::store_out(yb, (size_t)b * prev_ldy + prev_row, acc[b], y_dtype);
                     }
                 }
-#endif
                 tc_fence_before();
-                PROF_END(4)
             }
             have_prev = false;
             return true;
@@ -548,7 +539,6 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
             const int gshift = kGf4 ? 31 - __clz(p.g >> 7) : 0;   // GF4: log2 of the 128-code groups per scale
             uint4 sc_nxt = load_scales(srow, h, gshift);          // in flight during the table build / the previous tile's outputs
             if constexpr (kGf4) {
-                PROF_BEGIN
                 // ---- the pair table of this row (this thread fills the entries whose second code is in its half)
                 if (!(ok = quarter_sync())) break;      // both warps are done with the previous tile's lookups
                 const uint32_t c[8] = {cb0.x, cb0.y, cb0.z, cb0.w, cb1.x, cb1.y, cb1.z, cb1.w};
@@ -565,13 +555,10 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                         asm volatile("st.shared.u32 [%0], %1;" ::"r"(tb + (i * 16 + lo) * 128), "r"(e) : "memory");
                     }
                 fetch_codebook(tile + 1);
-                PROF_END(4)
             }
             // the previous tile's last groups have had the table build to finish; its sync also publishes the table
             const bool had_prev = have_prev;
-            { PROF_BEGIN
             if (!(ok = finish_prev())) break;
-            PROF_END(5) }
             if (kGf4 && !had_prev) { if (!(ok = quarter_sync())) break; }
 #pragma unroll
             for (int b = 0; b < NB; ++b) acc[b] = 0.f;
@@ -581,9 +568,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
             for (int i = 0; i < (NB + 31) / 32; ++i) xs_next[i] = (lane + 32 * i < B) ? p.xscale[lane + 32 * i] : 0.f;
             for (int j = 0; j < nsteps && ok; ++j) {
                 const int stage = wcount % kSW;
-                { PROF_BEGIN
                 ok = __all_sync(0xffffffffu, mbar_wait(wbar(warp, stage), (wcount / kSW) & 1, err));
-                PROF_END(1) }
                 if (!ok) break;
                 ++wcount;
                 const uint32_t slot = wring + stage * kWStage + lrow;
@@ -596,9 +581,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                     const unsigned short scale_raw = (unsigned short)(gi ? sc_cur.y : sc_cur.x);
                     const uint2 sc4 = gi ? make_uint2(sc_cur.z, sc_cur.w) : make_uint2(sc_cur.x, sc_cur.y);
                     // slot t % kRing is free once group t - kRing has been released
-                    { PROF_BEGIN
                     if (t_h - t_fold == (uint32_t)kRing && !(ok = fold_one())) break;
-                    PROF_END(2) }
                     const uint32_t t = t_h, s = t % kRing;
                     const uint32_t a_t = lane_t + (h * kRing + s) * C::kSlot;
                     uint4 w4[4];
@@ -633,9 +616,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                     uint32_t va[16], vb[16];
                     decode16(0, va);
                     decode16(1, vb);
-                    { PROF_BEGIN
                     hand_over();
-                    PROF_END(3) }
                     tmem_st16(a_t, va);
                     decode16(2, va);
                     tmem_st16(a_t + 16, vb);
@@ -660,13 +641,6 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
             for (int i = 0; i < (NB + 31) / 32; ++i) prev_xs[i] = xs_next[i];
         }
         if (ok) ok = finish_prev();
-#ifdef JQ_TA_PROF
-        if (blockIdx.x == 0 && q == 0 && lane == 0) {
-            long long *pr = reinterpret_cast<long long *>(status) + 8 + h * 8;
-            pc[0] = clock64() - pt_start;
-            for (int i = 0; i < 8; ++i) pr[i] = pc[i];
-        }
-#endif
     } else {
         // =============================== MMA issuers ===============================
         // Warps 8, 9: half 0, 1; warps 10, 11: a second issuer per half (kIssuers == 2).  With two issuers a half's
@@ -722,35 +696,22 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                     load_next();
                 }
                 const uint32_t s = n % xg.nstages;
-                { PROF_BEGIN
                 if (!(ok = mbar_wait(xbar(iss, s), (n / xg.nstages) & 1, err))) break;
-                PROF_END(1) }
                 const uint32_t t = C::kIssuers == 2 ? 2 * n + sub : n;     // the half's group count
                 const uint32_t slot = t % kRing, par = (t / kRing) & 1;
-                { PROF_BEGIN
                 if (!(ok = mbar_wait(abar(h, slot), par, err))) break;
-                PROF_END(2) }
                 tc_fence_after();
                 const uint32_t a_t = tmem + (h * kRing + slot) * C::kSlot;
                 const uint32_t d_t = kGf4 ? a_t + 64 : tmem + C::kAcc + (h * C::kIssuers + sub) * NB;
                 const uint32_t xb = ring + s * xg.chunk;
                 const bool first = mm.sg == h && mm.k == 0;                // E2M1: this issuer's first group of the tile
-                { PROF_BEGIN
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
                     mma_f16_ts(d_t, a_t + 8 * i, smem_desc(xb + 2 * i * lbo, lbo, 128), idesc, kGf4 ? (i > 0) : (i > 0 || !first));
                 mma_commit(dbar(h, slot));
                 mma_commit(xebar(iss, s));
-                PROF_END(3) }
                 advance(mm);
             }
-#ifdef JQ_TA_PROF
-            if (blockIdx.x == 0) {
-                long long *pr = reinterpret_cast<long long *>(status) + 8 + 16 + iss * 8;
-                pc[0] = clock64() - pt_start;
-                for (int i = 0; i < 8; ++i) pr[i] = pc[i];
-            }
-#endif
         }
     }
 
@@ -767,7 +728,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
     }
 }
 
-// ---- GF4, batch 1..2 on the CUDA cores ------------------------------------------------
+// ---- GF4, batch 1 on the CUDA cores (the template also covers two rows, where the tensor-memory kernel is faster) ----
 // Same tiles, same TMA weight ring, same per-row pair tables as the tensor-memory kernel above, but the
 // multiply-accumulate stays in the decode threads: lane = weight row, so all lanes of a warp need the same
 // activation values, which they read as broadcast 16-byte shared-memory loads (one wavefront per eight
@@ -1123,8 +1084,9 @@ static bool ta_shape_ok(int fmt, int N, int K, int g, int had) {
     return fmt == JQ_FMT_E2M1 && g == 32;
 }
 
-// batch 1..2 run on the CUDA cores when the prepared activation of one problem fits its shared-memory buffer
-static bool ta_use_lut(int B, int maxK) { return B <= 2 && (size_t)maxK * B * 2 <= (size_t)LutSmem::kXBytes; }
+// batch 1 runs on the CUDA cores when the prepared activation of one problem fits its shared-memory buffer
+// (K up to 12288); from two rows on the tensor-memory kernel is faster (decode7b: 1800 against 1090 tokens/s)
+static bool ta_use_lut(int B, int maxK) { return B == 1 && (size_t)maxK * 2 <= (size_t)LutSmem::kXBytes; }
 
 extern "C" size_t jq_ta_workspace_bytes(const jq_problem *ph, int n, int B) {
     if (!ph || n <= 0 || B < 1 || B > 64) return 0;
@@ -1254,8 +1216,7 @@ static int ta_dispatch(int fmt, int nb, int maxK, const TaProblem *probs_dev, co
 #define JQ_TA_ARGS probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, B, x_dtype, y_dtype, peers, status, st
     if (fmt == JQ_FMT_GF4) {
         if (ta_use_lut(B, maxK)) {
-            if (B == 1) return lut2_launch<1>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, x_dtype, y_dtype, peers, status, st);
-            return lut2_launch<2>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, x_dtype, y_dtype, peers, status, st);
+            return lut2_launch<1>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, grid, x_dtype, y_dtype, peers, status, st);
         }
         if (nb == 16) return ta_launch<JQ_FMT_GF4, 16>(JQ_TA_ARGS);
         return JQ_ERR_UNSUPPORTED;

@@ -72,10 +72,11 @@ def ta_max_batch(fmt_id: int) -> int:
 
 def ta_eligible(fmt_id: int, K: int, g: int, batch: int) -> bool:
     """Problems the TMA-fed kernels take.  GF4 (group size 128 * 2^k): every
-    batch -- 1 (and 2 while the prepared activation fits in shared memory) on
-    the CUDA-core pair-table loop, the rest on the tensor-memory kernel, 16
-    rows per pass.  E2M1 g32: batches from 9 rows on the tensor-memory kernel,
-    64 rows per pass (up to 8 rows the mma.sync row loops are faster)."""
+    batch -- one row (while the prepared activation fits in shared memory, K
+    up to 12288) on the CUDA-core pair-table loop, the rest on the
+    tensor-memory kernel, 16 rows per pass.  E2M1 g32: batches from 9 rows on
+    the tensor-memory kernel, 64 rows per pass (up to 8 rows the mma.sync row
+    loops are faster)."""
     if K % 256 or K < 512:
         return False
     if fmt_id == _lib.JQ_FMT_GF4:
