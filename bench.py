@@ -45,11 +45,16 @@ import torch  # noqa: E402
 
 HBM_NOMINAL_GBS = 8000.0
 PARITY_GATE = 1e-3
-# DRAM bytes (read + write) per algorithmic byte of the dominant kernel of each format, from one ncu capture each
-# on a smaller case of the same kernel (16 x 11008 x 4096 GF4: 449.2 MB for 378.1 MB, the excess being the TMA's
-# 128-byte L2 promotion of scale and codebook sectors; 16 x 8192 x 8192 E2M1: 608.6 MB for 604.5 MB); traffic
-# grows in proportion to the rows processed, so a full launch's traffic is this ratio times its algorithmic bytes.
-DRAM_TRAFFIC_RATIO = {"gf4": 449.177344 / 378.101760, "e2m1": 608.581888 / 604.504064}
+# DRAM bytes (read + write) per algorithmic byte of each dominant kernel, from one ncu capture each on a smaller
+# case of the same kernel (profiles/gf4_lut2_gf4_11008x4096_b1.md, profiles/gemm_ta_gf4_11008x4096_b16.md,
+# profiles/gemm_ta_e2m1_8192x8192_b16.md, profiles/gemv_grouped_e2m1_8192x8192.md); traffic grows in proportion
+# to the rows processed, so a full launch's traffic is this ratio times its algorithmic bytes.
+DRAM_TRAFFIC_RATIO = {
+    "gf4_lut2_kernel": (377.914624 + 4.447232) / 378.101760,
+    "gemm_ta_kernel<gf4>": (380.475136 + 8.024320) / 385.351680,
+    "gemm_ta_kernel<e2m1>": (622.311168 + 9.124096) / 612.368384,
+    "gemv_grouped_kernel": 608.581888 / 604.504064,      # E2M1; GF4 reaches this kernel only for ungrouped or short rows
+}
 
 WORKLOADS = {
     # name: (fmt, group, had_block, layers, [(label, N, K, count-per-layer)], init std, seed)
@@ -531,7 +536,7 @@ def main():
                 "gpu_launches": args.steps * (grp.launches_per_run or len(weights)),
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                              "frac": achieved / peak, "frac_of_8TBs": achieved / HBM_NOMINAL_GBS,
-                             "traffic": int(alg * DRAM_TRAFFIC_RATIO[fmt]) if (args.batch <= 8 or grp._ta) else None,
+                             "traffic": int(alg * DRAM_TRAFFIC_RATIO[kernel.split(" ")[0]]),
                              "peak_source": f"{how} copy bandwidth", "kernel": kernel,
                              "kernel_ms": k_ms, "algorithmic_bytes_per_launch": alg},
                 "parity": parity, "pack_seconds": meta["pack_seconds"], "exchange": exchange}

@@ -14,13 +14,11 @@
         if (_e != cudaSuccess) return JQ_ERR_CUDA_BASE - (int)_e; \
     } while (0)
 
+// Right after a launch: the thread's last CUDA error, read and thereby cleared.  CUDA has one slot per thread,
+// so an earlier unread asynchronous error of the process lands here too (stated in jq.h).
 static inline int jq_launch_status() {
-    cudaError_t e = cudaPeekAtLastError();
-    if (e != cudaSuccess) {
-        cudaGetLastError();
-        return JQ_ERR_CUDA_BASE - (int)e;
-    }
-    return JQ_OK;
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? JQ_OK : JQ_ERR_CUDA_BASE - (int)e;
 }
 
 static inline bool jq_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -737,6 +737,10 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
 // the group's fp16 scale in fp32.  At batch 1 this costs about 2.2 instructions and 0.75 shared-memory
 // wavefronts per code, where one 16-bit lookup per code costs 1.2 wavefronts; the tensor pipe, whose
 // K = 16 instructions have a floor of about 45 clocks whatever the batch, is not involved.
+// Per code a lane receives 2 bytes of looked-up pairs, 0.5 of packed weights and 2 of activations through
+// the shared-memory pipe (128 bytes per clock and SM).  A variant whose lanes carry two rows each and read
+// the activations once for both (8 warps instead of 16, same tables and ring) was slower: 950 against 1022
+// tokens/s on the 7B-shaped stack.
 constexpr int kLutQuarters = 2;                      // 32-row sets of a tile (each has its own pair table)
 constexpr int kLutTileM = 32 * kLutQuarters;
 constexpr int kLutSplit = 8;                         // warps that share a row set, each taking every 8th 256-code step
@@ -1018,6 +1022,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
     __syncthreads();
     if (tid == 0 && s_err) atomicExch(status, s_err);
 }
+
 
 }  // namespace jqta
 

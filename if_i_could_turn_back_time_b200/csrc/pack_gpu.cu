@@ -48,6 +48,7 @@ __global__ void __launch_bounds__(256) pack_e2m1_kernel(const float *__restrict_
     __half hs = __float2half_rn(__fdiv_rn(amax, 6.0f));
     float s = __half2float(hs);
     if (amax == 0.f || s == 0.f) { hs = __float2half_rn(1.0f); s = 1.0f; }
+    if (isinf(s)) { hs = __ushort_as_half((unsigned short)0x7bffu); s = 65504.0f; }   // absmax / 6 beyond fp16: largest finite scale, codes saturate
     if ((sl % per_group) == 0) scales[(size_t)n * (K / g) + sl / per_group] = hs;
     uint32_t words[4];
 #pragma unroll

@@ -267,6 +267,7 @@ extern "C" int jq_pack_e2m1_host(const float *W, int N, int K, int g, uint8_t *q
             uint16_t hb = double_to_half_bits((double)q6);
             float s = half_bits_to_float(hb);
             if (amax == 0.f || s == 0.f) { hb = 0x3c00u; s = 1.f; }
+            if (std::isinf(s)) { hb = 0x7bffu; s = 65504.f; }   // absmax / 6 beyond fp16: largest finite scale, codes saturate
             scales[(size_t)n * G + gi] = hb;
             for (int k = 0; k < g; ++k) put_code(q, gi * g + k, e2m1_code(w[gi * g + k] / s));
         }

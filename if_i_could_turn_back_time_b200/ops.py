@@ -85,6 +85,12 @@ def ta_eligible(fmt_id: int, K: int, g: int, batch: int) -> bool:
     return g == 32 and batch >= 9
 
 
+def _ta_aligned(*tensors) -> bool:
+    """The TMA-fed kernels read packed rows, codebooks and E2M1 scales in 16-byte pieces; a view that starts
+    elsewhere is served by the row loops instead."""
+    return all(t is None or t.data_ptr() % 16 == 0 for t in tensors)
+
+
 _ws_cache = {}
 _checked = False
 
@@ -175,7 +181,7 @@ def _linear_rows(x2, qweight, scales, codebook, bias, fmt_id, N, K, g, had, out_
     lib = _lib.load()
     Bt = x2.shape[0]
     y = torch.empty((Bt, N), dtype=_OUT[out_id] or x2.dtype, device=x2.device)
-    if ta_eligible(fmt_id, K, g, Bt):
+    if ta_eligible(fmt_id, K, g, Bt) and _ta_aligned(qweight, scales, codebook):
         return _linear_rows_ta(x2, qweight, scales, codebook, bias, fmt_id, N, K, g, had, y)
     xd, yd = _DT[x2.dtype], _DT[y.dtype]
     qw_p, sc_p, cb_p, bias_p = _ptr(qweight), _ptr(scales), _ptr(codebook), _ptr(bias)
@@ -320,7 +326,8 @@ class GroupedGemv:
         self._per_problem = False
         self._subs = []
         self._ta = []
-        use_ta = all(ta_eligible(w.spec.fmt_id, w.K, w.spec.group_size, batch) for w in weights)
+        use_ta = all(ta_eligible(w.spec.fmt_id, w.K, w.spec.group_size, batch)
+                     and _ta_aligned(w.qweight, w.scales, w.codebook) for w in weights)
         if use_ta:
             MAX_TA_BATCH = ta_max_batch(spec0.fmt_id)
             # through the TMA-fed kernels: one plan (and workspace) per sub-batch of at most 16 (GF4) or 64 (E2M1)

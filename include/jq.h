@@ -54,6 +54,11 @@ extern "C" {
 #define JQ_ERR_NOMEM (-8)
 #define JQ_ERR_SCRATCH_LIMIT (-9)
 #define JQ_ERR_CUDA_BASE (-1000) /* JQ_ERR_CUDA_BASE - cudaError_t */
+/* A launching entry point reads the calling thread's last CUDA error right after its launch (cudaGetLastError:
+ * reading clears it).  CUDA keeps one such slot per thread, so an asynchronous error left there earlier by other
+ * code of the process, and not yet read by it, is reported by -- and attributed to -- the next libjq launch; a
+ * caller that mixes libraries should read cudaGetLastError() itself before calling in if it needs to tell the two
+ * apart.  A non-sticky error never outlives the call that reports it. */
 
 /* element types of activations / outputs */
 #define JQ_F32 0
@@ -197,33 +202,47 @@ int jq_gemv_grouped_peers(const jq_problem *problems_dev, const void *plan_host,
                           const void *plan_dev, int x_dtype, int y_dtype, int npeer,
                           const int64_t *peer_delta, jq_stream_t stream);
 
-/* GF4 with per-row pair tables (B200 tensor memory / TMA kernels).  Same
- * operator as jq_gemv_gf4, i.e. the F.linear(x, W_bar, bias) of
- * Quantization_Experiments/layers.py:38, for group sizes of 128 * 2^k,
- * K % 256 == 0, K >= 512 and 1 <= B <= 16; every weight and scale stays exact
- * (only the fp32 summation order differs from the other kernels).  A byte of
- * packed codes indexes a 256-entry table of fp16 pairs that is built per
- * 128-row tile in shared memory, one bank column per weight row, so two codes
- * cost one conflict-free lookup; the packed rows arrive by 2-D tiled TMA.
- *   B <= 2 : the decode threads also multiply (fma.rn.f32.f16, fp32
- *            accumulation), reading the prepared activation by broadcast
- *            shared-memory loads;
- *   B >= 3 : the fp16 values go to tensor memory (tcgen05.st) as the A operand
- *            of tcgen05.mma kind::f16, one fp32 accumulator per 128-code group,
- *            read back (tcgen05.ld) and scaled in fp32.
+/* The TMA-fed kernels (B200 tensor memory).  Same operator as jq_gemv_gf4 /
+ * jq_gemv_e2m1, i.e. the F.linear(x, W_bar, bias) of
+ * Quantization_Experiments/layers.py:38, for K % 256 == 0, K >= 512,
+ * qweight / codebook / E2M1 scales 16-byte aligned, and
+ *   fmt GF4,  group sizes of 128 * 2^k, 1 <= B <= 16;
+ *   fmt E2M1, group size 32,            1 <= B <= 64.
+ * The packed rows arrive by 2-D tiled TMA (32-row x 128-byte boxes, 128-byte
+ * swizzle), a decode thread owns one weight row of a 128-row tile.
+ *   GF4: a byte of packed codes indexes a 256-entry table of fp16 pairs that is
+ *        built per tile in shared memory, one bank column per weight row, so
+ *        two codes cost one conflict-free lookup.  Every weight and every scale
+ *        stays exact; only the fp32 summation order differs from jq_gemv_gf4.
+ *        B == 1 (K <= 12288): the decode threads also multiply (fma.rn.f32.f16,
+ *        fp32 accumulation), reading the prepared activation by broadcast
+ *        shared-memory loads.  Otherwise the fp16 values go to tensor memory
+ *        (tcgen05.st) as the A operand of tcgen05.mma kind::f16, one fp32
+ *        accumulator per 128-code group, read back (tcgen05.ld) and scaled by
+ *        the group's fp16 scale in fp32.
+ *   E2M1: cvt.rn.f16x2.e2m1x2 per byte, then the group's fp16 scale is
+ *        multiplied in with mul.rn.f16x2 -- ONE fp16 rounding per weight that
+ *        jq_gemv_e2m1 does not have (its weights are exact): the results of the
+ *        two entry points differ by up to about 2^-11 relative per weight, well
+ *        inside the 1e-3 gate of the operator, and the dequantised matrix
+ *        (jq_dequant_e2m1) remains the exact one.  The whole row accumulates in
+ *        tensor memory (fp32).
  * A launch is preceded by a small kernel that rotates, normalises and rounds
  * the activation to fp16 once per problem (not once per CTA).  The workspace
  * (128-byte aligned, jq_ta_workspace_bytes) holds that prepared activation and
  * a status word at offset 0, which must be zero before the first use and is
- * only ever raised by the kernels (a bounded device-side wait that gave up
- * leaves JQ_ERR_TIMEOUT there and the kernel returns early with y partly
- * written).  jq_ta_status reads it (synchronising the stream) and, with
- * clear != 0, resets it.  Grouped form: jq_ta_plan (host only) validates the
- * problems, creates their tensor maps and writes jq_ta_plan_bytes(n) bytes
- * that the caller copies to the device (64-byte aligned); jq_gemm_ta_grouped
- * enqueues the two launches, with the peer-store all-gather of
- * jq_gemv_grouped_peers when npeer > 1.  problems_host[i].K alone is read by
- * jq_ta_workspace_bytes. */
+ * only ever raised by the kernels: every device-side wait is bounded (2^22
+ * polls or about 0.25 s); one that gives up leaves JQ_ERR_TIMEOUT there, the
+ * CTA's roles leave their loops, free tensor memory and the kernel returns
+ * early with y partly written.  The word is sticky across launches;
+ * jq_ta_status reads it (synchronising the stream) and, with clear != 0,
+ * resets it.  Grouped form: jq_ta_plan (host only) validates the problems,
+ * creates their tensor maps and writes jq_ta_plan_bytes(n) bytes that the
+ * caller copies to the device (64-byte aligned); jq_gemm_ta_grouped enqueues
+ * the two launches, with the peer-store all-gather of jq_gemv_grouped_peers
+ * when npeer > 1.  problems_host[i].K alone is read by jq_ta_workspace_bytes.
+ * Unsupported shapes return JQ_ERR_UNSUPPORTED, misaligned pointers
+ * JQ_ERR_BAD_ALIGN; nothing is launched then. */
 size_t jq_ta_workspace_bytes(const jq_problem *problems_host, int n, int B);
 size_t jq_ta_plan_bytes(int n);
 int jq_ta_plan(int fmt, const jq_problem *problems_host, int n, int B, void *workspace_dev,

@@ -92,13 +92,17 @@ def group_absmax(W: np.ndarray, g: int) -> np.ndarray:
 
 def quantize_e2m1(W: np.ndarray, g: int = 32):
     """fp32 W [N,K] -> (codes uint8 [N,K], scales fp16 [N,K/g]).
-    scale = fp16_rn(absmax/6), 1.0 for an all-zero group; u = w / fp32(scale)."""
+    scale = fp16_rn(absmax/6), 1.0 for an all-zero group, 65504 where that overflows; u = w / fp32(scale)."""
     W = np.asarray(W, dtype=np.float32)
     N, K = W.shape
     amax = group_absmax(W, g)
-    scales = (amax / np.float32(6.0)).astype(np.float16)
+    with np.errstate(over="ignore"):
+        scales = (amax / np.float32(6.0)).astype(np.float16)
     # a scale that underflows to zero in fp16 would divide by zero
     scales = np.where((amax == 0) | (scales == 0), np.float16(1.0), scales).astype(np.float16)
+    # one that overflows (absmax above 6 * 65504) would dequantise the whole group to inf / nan: largest finite
+    # fp16 instead, the codes saturate at +-6
+    scales = np.where(np.isinf(scales), np.float16(65504.0), scales).astype(np.float16)
     s32 = scales.astype(np.float32)
     u = (W.reshape(N, K // g, g) / s32[:, :, None]).astype(np.float32).reshape(N, K)
     return e2m1_round_codes(u), scales

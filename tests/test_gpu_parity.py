@@ -351,6 +351,25 @@ def test_k_256_stays_on_the_row_loops_at_every_batch():
         _check_gemv(pw, torch.randn(24, 256, generator=torch.Generator("cpu").manual_seed(1)).bfloat16())
 
 
+def test_misaligned_views_fall_back_to_the_row_loops():
+    """Scales and codebooks that start 8 bytes into an allocation cannot be read in 16-byte pieces by the TMA-fed
+    kernels; the row loops (2- and 4-byte alignment) serve the call."""
+    pw = jq.pack_weight(_weights(64, 1024, 4), jq.QuantSpec("gf4", 128, 128))
+
+    def shifted(t):
+        raw = torch.empty(t.numel() * t.element_size() + 8, dtype=torch.uint8, device=DEV)
+        v = raw[8:].view(t.dtype).view(t.shape)
+        v.copy_(t)
+        return v
+
+    off = jq.PackedWeight(pw.spec, pw.N, pw.K, pw.qweight.to(DEV), shifted(pw.scales), shifted(pw.codebook))
+    assert off.codebook.data_ptr() % 16 == 8
+    x = torch.randn(16, 1024, generator=torch.Generator("cpu").manual_seed(3)).bfloat16().to(DEV)
+    y = ops.linear(x, off, out_dtype=torch.float32)
+    y_ref = ops.linear(x, pw.to(DEV), out_dtype=torch.float32)
+    assert formats.rel_err(y.cpu().numpy(), y_ref.cpu().numpy()) <= 1e-5
+
+
 def test_large_batch_is_split_and_matches_the_row_loops():
     pw = jq.pack_weight(_weights(512, 1024, 3), jq.QuantSpec("e2m1", 32, 0)).to(DEV)
     x = torch.randn(130, 1024, generator=torch.Generator("cpu").manual_seed(2)).bfloat16().to(DEV)
@@ -632,6 +651,8 @@ def test_e2m1_gpu_packer_is_bit_identical_to_host_packer(N, K, g, had):
     W = _weights(N, K, N * 3 + K)
     W[0, :g] = 0
     W[1, :32] = torch.tensor([6, 0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25, -0.75, -5.0, -6] + [0] * 20) * 0.01
+    if not had:
+        W[2, :32] = torch.linspace(-5e5, 5e5, 32)      # absmax / 6 beyond fp16: clamped scale, saturated codes
     spec = jq.QuantSpec("e2m1", g, had)
     host = jq.pack_weight(W, spec)
     dev = jq.pack_weight(W.to(DEV), spec)

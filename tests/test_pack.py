@@ -39,6 +39,19 @@ def test_e2m1_ties_and_saturation():
     _same(pw, *formats.quantize_e2m1(W, 32), None)
 
 
+def test_e2m1_scale_beyond_fp16_is_clamped():
+    """absmax / 6 above the fp16 range: the scale is the largest finite fp16, the codes saturate, nothing becomes inf."""
+    W = np.zeros((2, 64), dtype=np.float32)
+    W[0, :32] = np.linspace(-5e5, 5e5, 32)          # absmax / 6 = 83333 > 65504
+    W[0, 32:] = np.linspace(-3.9e5, 3.9e5, 32)      # absmax / 6 = 65000 < 65504: untouched
+    W[1, :32] = 3.0e38
+    pw = jq.pack_weight(torch.from_numpy(W), jq.QuantSpec("e2m1", 32, 0))
+    codes, scales = formats.quantize_e2m1(W, 32)
+    _same(pw, codes, scales, None)
+    assert scales[0, 0] == np.float16(65504) and scales[1, 0] == np.float16(65504) and np.isfinite(scales).all()
+    assert np.isfinite(formats.dequant_e2m1(codes, scales, 32)).all()
+
+
 @pytest.mark.parametrize("N,K,g", [(12, 1024, 128), (6, 2048, 128), (4, 4096, 128), (9, 512, 64), (7, 300, 0),
                                     (10, 100, 0), (3, 784, 0)])
 def test_gf4_packer_bit_exact(N, K, g):
