@@ -1168,7 +1168,8 @@ static int validate_problem(int fmt, const void *qw, const void *scales, const v
     if (had != 0 && had != 128) return JQ_ERR_UNSUPPORTED;
     if (had && K % had) return JQ_ERR_BAD_SHAPE;
     if (!jq_aligned16(qw)) return JQ_ERR_BAD_ALIGN;
-    if (codebook && (reinterpret_cast<uintptr_t>(codebook) & 3u)) return JQ_ERR_BAD_ALIGN;
+    // codebook rows (32 bytes) are fetched with 16-byte copies; a base that is not 16-byte aligned would fault
+    if (codebook && !jq_aligned16(codebook)) return JQ_ERR_BAD_ALIGN;
     if (scales && (reinterpret_cast<uintptr_t>(scales) & 1u)) return JQ_ERR_BAD_ALIGN;
     return JQ_OK;
 }

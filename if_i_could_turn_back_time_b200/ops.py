@@ -86,8 +86,9 @@ def ta_eligible(fmt_id: int, K: int, g: int, batch: int) -> bool:
 
 
 def _ta_aligned(*tensors) -> bool:
-    """The TMA-fed kernels read packed rows, codebooks and E2M1 scales in 16-byte pieces; a view that starts
-    elsewhere is served by the row loops instead."""
+    """The TMA-fed kernels read E2M1 scales in 16-byte pieces (the row loops in 2- or 4-byte pieces); a view that
+    starts elsewhere is served by the row loops instead.  Packed rows and codebooks are 16-byte aligned on every
+    path (the library refuses anything else)."""
     return all(t is None or t.data_ptr() % 16 == 0 for t in tensors)
 
 

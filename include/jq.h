@@ -29,6 +29,9 @@
  *         fp16 [N, K/g] or absent (g = 0); w = fp32(codebook[n][code]) *
  *         fp32(scale)   (or just fp32(codebook[n][code]) when g = 0).
  * g is 0 (GF4 only) or a multiple of 32 that divides K.
+ * Alignment: qweight and codebook 16 bytes (rows are 16- / 32-byte multiples, so
+ * every row slice of an aligned matrix qualifies), scales 2 bytes; anything
+ * else is refused with JQ_ERR_BAD_ALIGN before a launch.
  */
 #ifndef JQ_H_
 #define JQ_H_

@@ -351,10 +351,11 @@ def test_k_256_stays_on_the_row_loops_at_every_batch():
         _check_gemv(pw, torch.randn(24, 256, generator=torch.Generator("cpu").manual_seed(1)).bfloat16())
 
 
-def test_misaligned_views_fall_back_to_the_row_loops():
-    """Scales and codebooks that start 8 bytes into an allocation cannot be read in 16-byte pieces by the TMA-fed
-    kernels; the row loops (2- and 4-byte alignment) serve the call."""
-    pw = jq.pack_weight(_weights(64, 1024, 4), jq.QuantSpec("gf4", 128, 128))
+def test_misaligned_scales_fall_back_to_the_row_loops_and_misaligned_codebooks_are_refused():
+    """E2M1 scales that start 8 bytes into an allocation cannot be read in 16-byte pieces by the tensor-memory
+    kernel; the row loops (2-byte alignment) serve the call.  A codebook that is not 16-byte aligned is refused
+    before any launch: every kernel fetches codebook rows with 16-byte copies."""
+    from if_i_could_turn_back_time_b200 import _lib
 
     def shifted(t):
         raw = torch.empty(t.numel() * t.element_size() + 8, dtype=torch.uint8, device=DEV)
@@ -362,12 +363,22 @@ def test_misaligned_views_fall_back_to_the_row_loops():
         v.copy_(t)
         return v
 
-    off = jq.PackedWeight(pw.spec, pw.N, pw.K, pw.qweight.to(DEV), shifted(pw.scales), shifted(pw.codebook))
-    assert off.codebook.data_ptr() % 16 == 8
+    pw = jq.pack_weight(_weights(64, 1024, 4), jq.QuantSpec("e2m1", 32, 0)).to(DEV)
+    off = jq.PackedWeight(pw.spec, pw.N, pw.K, pw.qweight, shifted(pw.scales), None)
+    assert off.scales.data_ptr() % 16 == 8
     x = torch.randn(16, 1024, generator=torch.Generator("cpu").manual_seed(3)).bfloat16().to(DEV)
     y = ops.linear(x, off, out_dtype=torch.float32)
-    y_ref = ops.linear(x, pw.to(DEV), out_dtype=torch.float32)
-    assert formats.rel_err(y.cpu().numpy(), y_ref.cpu().numpy()) <= 1e-5
+    y_rows = torch.cat([ops.linear(x[i:i + 8], pw, out_dtype=torch.float32) for i in range(0, 16, 8)])
+    # both went through the row loops (the aligned one on the mma.sync loop, the other on the FMA loop): same
+    # weights and activation rounding, fp32 summation order differs
+    assert formats.rel_err(y.cpu().numpy(), y_rows.cpu().numpy()) <= 1e-5
+
+    pg = jq.pack_weight(_weights(64, 1024, 4), jq.QuantSpec("gf4", 128, 128)).to(DEV)
+    bad = jq.PackedWeight(pg.spec, pg.N, pg.K, pg.qweight, pg.scales, shifted(pg.codebook))
+    for rows in (1, 4, 16):
+        with pytest.raises(_lib.JqError):
+            ops.linear(x[:rows], bad)
+    torch.cuda.synchronize()                                         # nothing was launched, the context is healthy
 
 
 def test_large_batch_is_split_and_matches_the_row_loops():
