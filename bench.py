@@ -46,9 +46,9 @@ import torch  # noqa: E402
 HBM_NOMINAL_GBS = 8000.0
 PARITY_GATE = 1e-3
 # DRAM bytes (read + write) per algorithmic byte of each dominant kernel, from one ncu capture each on a smaller
-# case of the same kernel (profiles/gf4_lut2_gf4_11008x4096_b1.md, profiles/gemm_ta_gf4_11008x4096_b16.md,
-# profiles/gemm_ta_e2m1_8192x8192_b16.md, profiles/gemv_grouped_e2m1_8192x8192.md); traffic grows in proportion
-# to the rows processed, so a full launch's traffic is this ratio times its algorithmic bytes.
+# case of the same kernel (16 x 11008 x 4096 GF4 at batch 1 and at batch 16, 16 x 8192 x 8192 E2M1 at batch 16 and
+# at batch 1); traffic grows in proportion to the rows processed, so a full launch's traffic is this ratio times its
+# algorithmic bytes.
 DRAM_TRAFFIC_RATIO = {
     "gf4_lut2_kernel": (377.914624 + 4.447232) / 378.101760,
     "gemm_ta_kernel<gf4>": (380.475136 + 8.024320) / 385.351680,
@@ -63,6 +63,7 @@ WORKLOADS = {
     "decode70b": ("e2m1", 32, 0, 80, [("qo", 8192, 8192, 2), ("kv", 1024, 8192, 2), ("gate_up", 28672, 8192, 2),
                                        ("down", 8192, 28672, 1)], 0.015, 4),
     "e2m1_4096": ("e2m1", 32, 0, 16, [("linear", 4096, 4096, 1)], 0.02, 1),
+    # the 70B-class attention projection alone: the batched kernel's sweep shape (16, 32, 64 rows)
     "e2m1_8192": ("e2m1", 32, 0, 16, [("linear", 8192, 8192, 1)], 0.02, 5),
     "gf4_11008": ("gf4", 128, 128, 16, [("linear", 11008, 4096, 1)], 0.02, 2),
 }

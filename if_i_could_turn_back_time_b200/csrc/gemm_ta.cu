@@ -183,28 +183,37 @@ __device__ __forceinline__ int act_exponent(float amax, bool had) {
 // layout of the MMA with a piece stride of 16 B bytes: row n of piece c sits at (c B + n) 16 bytes.  The MMA
 // always reads 16 rows; rows >= B are whatever follows (the next pieces), and their accumulator columns
 // are never read.
-__global__ void __launch_bounds__(256) ta_prepare_kernel(const TaProblem *probs, TaProblem single, int B,
-                                                          int x_dtype) {
-    __shared__ float sred[8];
+// The second pass is a chain of load -> rotate -> store per 128-element block and warp, and its latency is what a
+// decode step waits for before the main kernel can start.  With one or two batch rows there are few blocks: 32 warps
+// each (K = 11008: 3 rounds instead of 11; 4.5 us less per 7B-shaped step).  With many batch rows 8 warps per block
+// keep more rows resident per SM.
+template <int kPrepThreads>
+__global__ void __launch_bounds__(kPrepThreads) ta_prepare_kernel(const TaProblem *probs, TaProblem single, int B,
+                                                                   int x_dtype) {
+    constexpr int kWarps = kPrepThreads / 32;
+    __shared__ float sred[kWarps];
     __shared__ int sexp;
     const int pi = blockIdx.x / B, b = blockIdx.x % B;
     const TaProblem p = probs ? probs[pi] : single;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float m = 0.f;
-    for (int k = tid; k < p.K; k += 256) m = fmaxf(m, fabsf(jq::load_act(p.x, (size_t)b * p.K + k, x_dtype)));
+    for (int k = tid; k < p.K; k += kPrepThreads) m = fmaxf(m, fabsf(jq::load_act(p.x, (size_t)b * p.K + k, x_dtype)));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if (lane == 0) sred[warp] = m;
     __syncthreads();
-    if (tid == 0) {
-        float mm = 0.f;
-        for (int w = 0; w < 8; ++w) mm = fmaxf(mm, sred[w]);
-        sexp = act_exponent(mm, p.had != 0);
-        p.xscale[b] = __uint_as_float((uint32_t)(127 + sexp) << 23);
+    if (warp == 0) {
+        float mm = lane < kWarps ? sred[lane] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+        if (lane == 0) {
+            sexp = act_exponent(mm, p.had != 0);
+            p.xscale[b] = __uint_as_float((uint32_t)(127 + sexp) << 23);
+        }
     }
     __syncthreads();
     const float down = __uint_as_float((uint32_t)(127 - sexp) << 23);
-    for (int blk = warp; blk * 128 < p.K; blk += 8) {
+    for (int blk = warp; blk * 128 < p.K; blk += kWarps) {
         float v[4];
         const int k0 = blk * 128 + lane * 4;
 #pragma unroll
@@ -675,41 +684,48 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
             Walk ld = {tile_lo, 0, -1, 0, 0, 0, nullptr};
             open_tile(ld);
             Walk mm = ld;
-            uint32_t n_ld = 0;
+            // The issuing thread is a single lane running dependent scalar code on a scheduler it shares with two
+            // decode warps, so every instruction of this loop costs several clocks: ring positions and parities
+            // are carried along instead of being divided out of counters, and the operand descriptor is formed
+            // once per group.
+            uint32_t ld_s = 0;                          // stage the next load goes to
             auto load_next = [&]() {
                 if (ld.tile < tile_hi) {
-                    const uint32_t s = n_ld % xg.nstages;
                     const int G = 2 * ld.sg + (C::kIssuers == 2 ? sub : ld.k);
-                    mbar_expect_tx(xbar(iss, s), xg.chunk);
-                    bulk_g2s(ring + s * xg.chunk, ld.xp + (size_t)G * xg.chunk, xg.chunk, xbar(iss, s));
+                    mbar_expect_tx(xbar(iss, ld_s), xg.chunk);
+                    bulk_g2s(ring + ld_s * xg.chunk, ld.xp + (size_t)G * xg.chunk, xg.chunk, xbar(iss, ld_s));
                     advance(ld);
                 }
-                ++n_ld;
+                ld_s = (ld_s + 1 == (uint32_t)xg.nstages) ? 0 : ld_s + 1;
             };
             for (int i = 0; i < xg.nstages; ++i) load_next();
             bool ok = true;
+            uint32_t cs = 0, cpar = 0;                  // stage and phase parity of the group being multiplied
+            uint32_t rs = 0, rpar = 0;                  // stage and phase parity of the group whose stage is refilled next
+            uint32_t slot = (uint32_t)sub % kRing, spar = 0;   // A slot of this issuer's next group (the half's group count t = kIssuers n + sub)
+            const uint32_t desc_step = (2 * lbo) >> 4;  // descriptor address field per K = 16 slice
             for (uint32_t n = 0; mm.tile < tile_hi && ok; ++n) {
                 // the stage whose MMAs were issued xg.lag groups ago is free by now: refill it
                 if (n >= (uint32_t)xg.lag) {
-                    const uint32_t m = n - xg.lag;
-                    if (!(ok = mbar_wait(xebar(iss, m % xg.nstages), (m / xg.nstages) & 1, err))) break;
+                    if (!(ok = mbar_wait(xebar(iss, rs), rpar, err))) break;
                     load_next();
+                    if (++rs == (uint32_t)xg.nstages) { rs = 0; rpar ^= 1; }
                 }
-                const uint32_t s = n % xg.nstages;
-                if (!(ok = mbar_wait(xbar(iss, s), (n / xg.nstages) & 1, err))) break;
-                const uint32_t t = C::kIssuers == 2 ? 2 * n + sub : n;     // the half's group count
-                const uint32_t slot = t % kRing, par = (t / kRing) & 1;
-                if (!(ok = mbar_wait(abar(h, slot), par, err))) break;
+                if (!(ok = mbar_wait(xbar(iss, cs), cpar, err))) break;
+                if (!(ok = mbar_wait(abar(h, slot), spar, err))) break;
                 tc_fence_after();
                 const uint32_t a_t = tmem + (h * kRing + slot) * C::kSlot;
                 const uint32_t d_t = kGf4 ? a_t + 64 : tmem + C::kAcc + (h * C::kIssuers + sub) * NB;
-                const uint32_t xb = ring + s * xg.chunk;
+                const uint64_t desc0 = smem_desc(ring + cs * xg.chunk, lbo, 128);
                 const bool first = mm.sg == h && mm.k == 0;                // E2M1: this issuer's first group of the tile
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-                    mma_f16_ts(d_t, a_t + 8 * i, smem_desc(xb + 2 * i * lbo, lbo, 128), idesc, kGf4 ? (i > 0) : (i > 0 || !first));
+                    mma_f16_ts(d_t, a_t + 8 * i, desc0 + (uint64_t)(i * desc_step), idesc, kGf4 ? (i > 0) : (i > 0 || !first));
                 mma_commit(dbar(h, slot));
-                mma_commit(xebar(iss, s));
+                mma_commit(xebar(iss, cs));
+                if (++cs == (uint32_t)xg.nstages) { cs = 0; cpar ^= 1; }
+                slot += C::kIssuers;
+                if (slot >= (uint32_t)kRing) { slot -= kRing; spar ^= 1; }
                 advance(mm);
             }
         }
@@ -1185,7 +1201,8 @@ static int ta_launch(const TaProblem *probs_dev, const CUtensorMap *maps_dev, co
                      const int *cta_first, int grid, int B, int x_dtype, int y_dtype, const jqta::PeerInfo &peers,
                      int *status, cudaStream_t st) {
     const int nblk = (nprob ? nprob : 1) * B;
-    ta_prepare_kernel<<<nblk, 256, 0, st>>>(probs_dev, single, B, x_dtype);
+    if (B <= 2) ta_prepare_kernel<1024><<<nblk, 1024, 0, st>>>(probs_dev, single, B, x_dtype);
+    else ta_prepare_kernel<256><<<nblk, 256, 0, st>>>(probs_dev, single, B, x_dtype);
     int s = jq_launch_status();
     if (s) return s;
     auto kern = gemm_ta_kernel<FMT, NB>;
@@ -1202,7 +1219,8 @@ static int lut2_launch(const TaProblem *probs_dev, const CUtensorMap *maps_dev, 
                        const CUtensorMap &single_map, int nprob, const int *tile_start, const int *cta_first, int grid,
                        int x_dtype, int y_dtype, const jqta::PeerInfo &peers, int *status, cudaStream_t st) {
     const int nblk = (nprob ? nprob : 1) * B;
-    ta_prepare_kernel<<<nblk, 256, 0, st>>>(probs_dev, single, B, x_dtype);
+    if (B <= 2) ta_prepare_kernel<1024><<<nblk, 1024, 0, st>>>(probs_dev, single, B, x_dtype);
+    else ta_prepare_kernel<256><<<nblk, 256, 0, st>>>(probs_dev, single, B, x_dtype);
     int s = jq_launch_status();
     if (s) return s;
     auto kern = gf4_lut2_kernel<B>;

@@ -7,6 +7,8 @@ that it composes with torch's dispatcher (fake tensors, export).
 from __future__ import annotations
 
 import ctypes
+import threading
+import warnings
 from typing import List, Optional, Sequence
 
 import numpy as np
@@ -92,8 +94,15 @@ def _ta_aligned(*tensors) -> bool:
     return all(t is None or t.data_ptr() % 16 == 0 for t in tensors)
 
 
-_ws_cache = {}
+_tls = threading.local()   # every host thread has its own scratch buffers: calls from different threads never share one
 _checked = False
+
+
+def _ws_cache() -> dict:
+    d = getattr(_tls, "ws", None)
+    if d is None:
+        d = _tls.ws = {}
+    return d
 
 
 def set_checked(on: bool) -> None:
@@ -111,13 +120,21 @@ def _workspace(device, nbytes: int, kind: str = "gemv") -> torch.Tensor:
     its own.  The family with a status word at offset 0 ("ta") never shares
     a buffer with the split-K partial sums, and starts zeroed."""
     key = (device, torch.cuda.current_stream(device).cuda_stream, kind)
-    t = _ws_cache.get(key)
+    cache = _ws_cache()
+    t = cache.get(key)
     if t is None or t.numel() < nbytes:
         if t is not None and kind != "gemv" and check_status(raise_on_error=False):
             raise RuntimeError("a device-side wait gave up in an earlier call (status word raised)")
         t = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _ws_cache[key] = t
+        cache[key] = t
     return t
+
+
+def reserve_workspace(device, nbytes: int, kind: str = "ta") -> None:
+    """Allocate this thread's scratch for (device, current stream, kernel family) ahead of time, e.g. before a
+    CUDA-graph capture or a region that must not allocate: kind "gemv" = split-K partial sums of the row loops,
+    "ta" = prepared activations and status word of the TMA-fed kernels."""
+    _workspace(torch.device(device), nbytes, kind)
 
 
 def check_status(raise_on_error: bool = True) -> int:
@@ -129,7 +146,7 @@ def check_status(raise_on_error: bool = True) -> int:
     dev = torch.device("cuda", torch.cuda.current_device())
     stream = torch.cuda.current_stream(dev).cuda_stream
     worst = 0
-    ws = _ws_cache.get((dev, stream, "ta"))
+    ws = _ws_cache().get((dev, stream, "ta"))
     if ws is not None:
         worst = min(worst, lib.jq_ta_status(_ptr(ws), 1, _stream()))
     if worst and raise_on_error:
@@ -412,6 +429,7 @@ class GroupedGemv:
             if self._symm is not None:
                 _lib.check(st, "jq_gemv_grouped_peers")
             # batch x K too large for one staged activation per CTA: one (split-K) launch per matrix instead
+            warnings.warn("GroupedGemv: this batch x K does not fit a grouped launch; running one launch per matrix")
             self._per_problem = True
         for w, x, y, b, nf, ro in zip(self.weights, self.xs, self.ys, self.biases, self.full_rows, self.row_offsets):
             y[:, ro:ro + w.N].copy_(linear(x, w, b))

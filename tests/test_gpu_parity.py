@@ -381,6 +381,27 @@ def test_misaligned_scales_fall_back_to_the_row_loops_and_misaligned_codebooks_a
     torch.cuda.synchronize()                                         # nothing was launched, the context is healthy
 
 
+@pytest.mark.parametrize("fmt,g,had,B", [("gf4", 128, 128, 1), ("gf4", 128, 128, 16), ("e2m1", 32, 0, 1), ("e2m1", 32, 0, 16)])
+def test_linear_replays_from_a_cuda_graph(fmt, g, had, B):
+    """After one warm-up call on the capture stream (which allocates that stream's scratch) a call enqueues
+    kernels only: it can be captured and replayed with new inputs."""
+    pw = jq.pack_weight(_weights(192, 1024, 12), jq.QuantSpec(fmt, g, had)).to(DEV)
+    gen = torch.Generator("cpu").manual_seed(B)
+    x = torch.randn(B, 1024, generator=gen).bfloat16().to(DEV)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ops.linear(x, pw)
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        y = ops.linear(x, pw)
+    x2 = torch.randn(B, 1024, generator=gen).bfloat16().to(DEV)
+    x.copy_(x2)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y, ops.linear(x2, pw))
+
+
 def test_large_batch_is_split_and_matches_the_row_loops():
     pw = jq.pack_weight(_weights(512, 1024, 3), jq.QuantSpec("e2m1", 32, 0)).to(DEV)
     x = torch.randn(130, 1024, generator=torch.Generator("cpu").manual_seed(2)).bfloat16().to(DEV)

@@ -72,3 +72,22 @@ def test_status_helpers_without_any_workspace():
     assert ops._checked is True
     ops.set_checked(False)
     assert ops._checked is False
+
+
+def test_scratch_buffers_are_per_thread():
+    """Calls from different host threads never share a workspace: the cache lives in thread-local storage."""
+    import threading
+    from if_i_could_turn_back_time_b200 import ops
+    mine = ops._ws_cache()
+    mine["probe"] = 1
+    seen = {}
+
+    def other():
+        seen["cache"] = ops._ws_cache()
+        seen["empty"] = "probe" not in seen["cache"]
+
+    t = threading.Thread(target=other)
+    t.start()
+    t.join()
+    del mine["probe"]
+    assert seen["empty"] and seen["cache"] is not mine
