@@ -253,11 +253,13 @@ struct Cols {
     // whatever the accumulator; threads of different warps issue in parallel.  At N = 64 two issuers already
     // saturate the pipe's arithmetic.
     static constexpr int kIssuers = (!kGf4 && NB == 64) ? 1 : 2;
-    static constexpr int kRing = (kGf4 || NB <= 16) ? 3 : 2;       // groups a half may have in flight
+    static constexpr int kRing = 3;                                // groups a half may have in flight
     static constexpr int kSlot = 64 + (kGf4 ? NB : 0);
     static constexpr int kAcc = 2 * kRing * kSlot;                 // E2M1: accumulator of (half h, issuer i) at kAcc + (h * kIssuers + i) * NB
-    static constexpr int kExchange = kAcc + (kGf4 ? 0 : 2 * kIssuers * NB);
-    static_assert(kExchange + NB <= 512, "tensor memory");
+    // GF4 hands the second half's sums to the first half's threads through NB more columns; E2M1 needs all 512
+    // columns at 32 and 64 rows and uses shared memory for that (GF4 has none to spare)
+    static constexpr int kExchange = kAcc;
+    static_assert(kGf4 ? kExchange + NB <= 512 : kAcc + 2 * kIssuers * NB <= 512, "tensor memory");
 };
 
 template <int FMT>
@@ -267,8 +269,10 @@ struct Smem {
     static constexpr int kWRing = kGf4 ? kTabBytes : 0;
     static constexpr int kSW = 2;       // stages of a decode warp's weight ring (four did not change anything: the ring is not what the decode threads wait for)
     static constexpr int kXRing = kWRing + kDecodeWarps * kSW * kWStage;
-    static constexpr int kXBytes = kGf4 ? 32 * 1024 : 144 * 1024;   // E2M1 has no tables: room for 64 batch rows per group
-    static constexpr int kBars = kXRing + kXBytes + 512;            // + what the MMA reads past the last chunk (rows >= B)
+    static constexpr int kXBytes = kGf4 ? 32 * 1024 : 96 * 1024;    // E2M1 has no tables: three stages of 64 batch rows per issuer
+    static constexpr int kExch = kXRing + kXBytes + 512;            // + what the MMA reads past the last chunk (rows >= B)
+    static constexpr int kExchBytes = kGf4 ? 0 : 2 * kTileM * 64 * 4;   // E2M1: second half's sums, [tile parity][batch row][tile row] fp32
+    static constexpr int kBars = kExch + kExchBytes;
     static constexpr int kNumBars = kDecodeWarps * 4 + 4 * 3 + 2 * 4 * kXMaxStages + 4;   // weights, A full, MMAs done, x full/free per issuer, quarter sync
     static constexpr int kBytes = kBars + kNumBars * 8 + 1024;      // + slack for the 1 KB alignment of the base (TMA swizzle)
 };
@@ -429,6 +433,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
         void *prev_y = nullptr;
         float prev_xs[(NB + 31) / 32];   // lane l holds 2^e of batch rows l, l + 32 (loaded at the start of the tile)
 
+        uint32_t fin_count = 0;     // finished tiles so far (parity picks the E2M1 exchange buffer)
         int pend_slot = -1;         // slot of the group whose tensor-memory stores are issued but not yet handed over
         auto hand_over = [&]() {
             if (pend_slot >= 0) {
@@ -486,15 +491,27 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                     }
                 }
             }
+            // E2M1: two buffers by tile parity, so that the second half (which does not meet the first again until
+            // the end of the next tile) never overwrites sums that are still to be read; column b of the buffer is
+            // 128 consecutive floats, one per tile row: conflict-free for a warp
+            float *exch = reinterpret_cast<float *>(smem_raw + (sbase - smem_u32(smem_raw)) + S::kExch) +
+                          (fin_count & 1) * (kTileM * 64) + r;
+            ++fin_count;
             if (h == 1) {
+                if constexpr (kGf4) {
 #pragma unroll
-                for (int c = 0; c < NB; c += 16) {
-                    uint32_t v[16];
+                    for (int c = 0; c < NB; c += 16) {
+                        uint32_t v[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(acc[c + i]);
-                    tmem_st16(lane_t + C::kExchange + c, v);
+                        for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(acc[c + i]);
+                        tmem_st16(lane_t + C::kExchange + c, v);
+                    }
+                    tmem_wait_st();
+                } else {
+#pragma unroll
+                    for (int b = 0; b < NB; ++b)
+                        exch[b * kTileM] = acc[b];
                 }
-                tmem_wait_st();
             }
             tc_fence_before();
             if (!quarter_sync()) return false;
@@ -504,8 +521,13 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
 #pragma unroll
                 for (int c = 0; c < NB; c += 16) {
                     uint32_t v[16];
-                    tmem_ld16(lane_t + C::kExchange + c, v);
-                    tmem_wait_ld();
+                    if constexpr (kGf4) {
+                        tmem_ld16(lane_t + C::kExchange + c, v);
+                        tmem_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(exch[(c + i) * kTileM]);
+                    }
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const int b = c + i;
