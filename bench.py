@@ -50,9 +50,9 @@ PARITY_GATE = 1e-3
 # at batch 1); traffic grows in proportion to the rows processed, so a full launch's traffic is this ratio times its
 # algorithmic bytes.
 DRAM_TRAFFIC_RATIO = {
-    "gf4_lut2_kernel": (377.914624 + 4.447232) / 378.101760,
-    "gemm_ta_kernel<gf4>": (380.475136 + 8.024320) / 385.351680,
-    "gemm_ta_kernel<e2m1>": (622.311168 + 9.124096) / 612.368384,
+    "gf4_lut2_kernel": (377.961216 + 5.431552) / 378.101760,
+    "gemm_ta_kernel<gf4>": (380.471808 + 8.067328) / 385.351680,
+    "gemm_ta_kernel<e2m1>": (621.232640 + 6.949376) / 612.368384,
     "gemv_grouped_kernel": 608.581888 / 604.504064,      # E2M1; GF4 reaches this kernel only for ungrouped or short rows
 }
 
