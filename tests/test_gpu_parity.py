@@ -610,13 +610,16 @@ def test_grouped_launch_tiles_k_when_batch_times_k_exceeds_shared_memory(B, had)
         assert formats.rel_err(y.cpu().numpy(), ref.cpu().numpy()) <= 2e-6
 
 
-@pytest.mark.parametrize("fmt,g,had,B", [("gf4", 128, 128, 1), ("e2m1", 32, 0, 1), ("e2m1", 32, 128, 4),
-                                         ("e2m1", 32, 0, 7), ("gf4", 128, 128, 5)])
-def test_grouped_row_shards_and_peer_copies_on_one_gpu(fmt, g, had, B):
+@pytest.mark.parametrize("fmt,g,had,B,kmin", [("gf4", 128, 128, 1, 256), ("e2m1", 32, 0, 1, 256), ("e2m1", 32, 128, 4, 256),
+                                              ("e2m1", 32, 0, 7, 256), ("gf4", 128, 128, 5, 256),
+                                              ("gf4", 128, 128, 1, 512), ("gf4", 128, 128, 5, 512),
+                                              ("gf4", 128, 0, 16, 512), ("e2m1", 32, 0, 16, 512), ("e2m1", 32, 128, 40, 512)])
+def test_grouped_row_shards_and_peer_copies_on_one_gpu(fmt, g, had, B, kmin):
     """Two row shards of each matrix run as two grouped launches into full-width outputs; the second
     launch also writes every result into a second buffer through the peer-copy path (here a local
-    buffer stands in for a peer GPU's).  Both must equal the unsharded result bit for bit."""
-    shapes = [(512, 1024), (96, 2048), (1000, 256)]
+    buffer stands in for a peer GPU's).  Both must equal the unsharded result bit for bit.  With a
+    K = 256 matrix in the set the row loops serve the group, with K >= 512 the TMA-fed kernels."""
+    shapes = [(512, 1024), (96, 2048), (1000, kmin)]
     spec = jq.QuantSpec(fmt, g, had)
     full = [jq.pack_weight(_weights(n, k, n + k), spec) for n, k in shapes]
     gen = torch.Generator("cpu").manual_seed(4)
@@ -636,6 +639,7 @@ def test_grouped_row_shards_and_peer_copies_on_one_gpu(fmt, g, had, B):
         target = mirror if rank == 0 else halves[0].y_arena
         grp._peer_delta = np.array([0, target.data_ptr() - grp.y_arena.data_ptr()], dtype=np.int64)
         grp.run()
+        assert bool(grp._ta) == (kmin >= 512) and grp.status() == 0
     torch.cuda.synchronize()
     for i, r in enumerate(ref):
         assert torch.equal(halves[0].ys[i], r)                      # own half + the half pushed by "rank 1"
