@@ -168,6 +168,13 @@ __device__ __forceinline__ uint32_t dp4a_u(uint32_t a, uint32_t b, uint32_t c) {
     return d;
 }
 
+// Programmatic dependent launch: the main kernels are launched while the activation preparation in front of them
+// is still running; everything they do before pdl_wait() (barrier set-up, problem look-ups, the first weight boxes)
+// overlaps it, everything that reads the prepared activation comes after.  Without the launch attribute both are
+// no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // e with amax * 2^-e below 2^15 after the rotation's worst-case growth (the rule of the GEMV kernels)
 __device__ __forceinline__ int act_exponent(float amax, bool had) {
     uint32_t bits = __float_as_uint(amax);
@@ -193,6 +200,7 @@ __global__ void __launch_bounds__(kPrepThreads) ta_prepare_kernel(const TaProble
     constexpr int kWarps = kPrepThreads / 32;
     __shared__ float sred[kWarps];
     __shared__ int sexp;
+    pdl_launch_dependents();
     const int pi = blockIdx.x / B, b = blockIdx.x % B;
     const TaProblem p = probs ? probs[pi] : single;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -351,7 +359,18 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
     // problem in registers and goes back to global memory only for a tile beyond that problem's last one.
     auto problem_at = [&](int &pi, int &t_end, int tile, TaProblem &p) {
         if (nprob == 0) { p = single; t_end = 0x7fffffff; return; }
-        while (pi + 1 < nprob && tile_start[pi + 1] <= tile) ++pi;
+        if (t_end < 0) {
+            // first look-up of a walker: bisect (a step's list can hold hundreds of problems, and a scan from the
+            // first one is a chain of dependent global loads, 0.2 us each, in front of the last CTAs' first tile)
+            int lo = 0, hi = nprob - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (tile_start[mid] <= tile) lo = mid; else hi = mid - 1;
+            }
+            pi = lo;
+        } else {
+            while (pi + 1 < nprob && tile_start[pi + 1] <= tile) ++pi;
+        }
         p = probs[pi];
         t_end = tile_start[pi + 1];
     };
@@ -560,6 +579,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
         int c_pi = 0, c_tend = -1;
         TaProblem p = single;
         fetch_codebook(tile_lo);
+        pdl_wait();                 // from here on the prepared activation and its row factors are read
         bool ok = true;
         for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
             if (tile >= c_tend) problem_at(c_pi, c_tend, tile, p);
@@ -720,6 +740,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) gemm_ta_kernel(const TaProblem 
                 }
                 ld_s = (ld_s + 1 == (uint32_t)xg.nstages) ? 0 : ld_s + 1;
             };
+            pdl_wait();
             for (int i = 0; i < xg.nstages; ++i) load_next();
             bool ok = true;
             uint32_t cs = 0, cpar = 0;                  // stage and phase parity of the group being multiplied
@@ -846,7 +867,18 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
     // in registers and goes back to global memory only when a tile lies beyond that problem's last tile.
     auto problem_at = [&](int &pi, int &t_end, int tile, TaProblem &p) {
         if (nprob == 0) { p = single; t_end = 0x7fffffff; return; }
-        while (pi + 1 < nprob && tile_start[pi + 1] <= tile) ++pi;
+        if (t_end < 0) {
+            // first look-up of a walker: bisect (a step's list can hold hundreds of problems, and a scan from the
+            // first one is a chain of dependent global loads, 0.2 us each, in front of the last CTAs' first tile)
+            int lo = 0, hi = nprob - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (tile_start[mid] <= tile) lo = mid; else hi = mid - 1;
+            }
+            pi = lo;
+        } else {
+            while (pi + 1 < nprob && tile_start[pi + 1] <= tile) ++pi;
+        }
         p = probs[pi];
         t_end = tile_start[pi + 1];
     };
@@ -945,6 +977,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) gf4_lut2_kernel(const TaProble
     int c_pi = 0, c_tend = -1, x_pi = -1;
     TaProblem p = single;
     fetch_codebook(tile_lo);
+    pdl_wait();                     // from here on the prepared activation and its row factors are read
     bool ok = true;
     int tparity = 0;
     for (int tile = tile_lo; tile < tile_hi && ok; ++tile, tparity ^= 1) {
@@ -1071,6 +1104,7 @@ using namespace jqta;
 // largest K, 0, 0, 0],
 // tile_start[n + 1], cta_first[grid + 1], padding to 64 bytes, TaProblem[n], padding to 64 bytes, CUtensorMap[n]
 static const int kTaMagic = 0x4a515441;
+static const double kTileCost = 384, kProblemCost = 2048;   // in codes of one row: fixed time per tile / per problem
 static const int kTaHeader = 12;
 
 // MMA N: GF4 keeps one accumulator per group and slot (up to 16 columns); E2M1 one per half (up to 64)
@@ -1200,21 +1234,36 @@ extern "C" int jq_ta_plan(int fmt, const jq_problem *ph, int n, int B, void *wor
         const int tiles = (ph[i].N + tile_m - 1) / tile_m;
         tp[i].tile0 = tile_start[i];
         tile_start[i + 1] = tile_start[i] + tiles;
-        total += (double)tiles * ph[i].K;
+        total += (double)tiles * (ph[i].K + kTileCost) + kProblemCost;
     }
-    // contiguous tile ranges of (nearly) equal packed bytes: cut where the running cost passes c * total / grid
+    // contiguous tile ranges of (nearly) equal cost: cut where the running cost passes c * total / grid.  A tile
+    // costs its packed bytes plus a fixed part (table build, two syncs, outputs), a problem's first tile also the
+    // switch of the activation buffer: with bytes alone a CTA of short rows ran 10 % longer than one of long rows.
     int cta = 0;
     double acc = 0;
     cta_first[0] = 0;
     for (int i = 0; i < n; ++i)
         for (int t = tile_start[i]; t < tile_start[i + 1]; ++t) {
-            while (cta + 1 < grid && acc + 0.5 * ph[i].K >= total * (cta + 1) / grid) cta_first[++cta] = t;
-            acc += ph[i].K;
+            const double c = ph[i].K + kTileCost + (t == tile_start[i] ? kProblemCost : 0);
+            while (cta + 1 < grid && acc + 0.5 * c >= total * (cta + 1) / grid) cta_first[++cta] = t;
+            acc += c;
         }
     while (cta < grid) cta_first[++cta] = tile_start[n];
     h[0] = kTaMagic; h[1] = n; h[2] = grid; h[3] = ta_cols(fmt, B); h[4] = (int)moff; h[5] = B; h[6] = fmt; h[7] = (int)poff;
     h[8] = maxK; h[9] = h[10] = h[11] = 0;
     return JQ_OK;
+}
+
+// launch configuration of a main kernel: allowed to start while the preparation kernel in front of it still runs
+static void ta_pdl_config(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, int grid, int threads, int smem, cudaStream_t st) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
 }
 
 template <int FMT, int NB>
@@ -1231,8 +1280,11 @@ static int ta_launch(const TaProblem *probs_dev, const CUtensorMap *maps_dev, co
     constexpr int smem = Smem<FMT>::kBytes;
     static_assert(smem <= 227 * 1024, "shared memory");
     JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<grid, kTaThreads, smem, st>>>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, B, y_dtype, peers,
-                                         status);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    ta_pdl_config(cfg, attr, grid, kTaThreads, smem, st);
+    JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, B, y_dtype,
+                                   peers, status));
     return jq_launch_status();
 }
 
@@ -1249,8 +1301,11 @@ static int lut2_launch(const TaProblem *probs_dev, const CUtensorMap *maps_dev, 
     constexpr int smem = LutSmem::kBytes;
     static_assert(smem <= 227 * 1024, "shared memory");
     JQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<grid, kLutThreads, smem, st>>>(probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, y_dtype,
-                                          peers, status);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    ta_pdl_config(cfg, attr, grid, kLutThreads, smem, st);
+    JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, probs_dev, maps_dev, single, single_map, nprob, tile_start, cta_first, y_dtype,
+                                   peers, status));
     return jq_launch_status();
 }
 

@@ -1112,11 +1112,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_grouped_kernel(const jq_prob
     const SmemLayout L = carve<FMT, B, DEPTH>(smem, xcap);
     int rg = cta_first[blockIdx.x];
     const int rg_end = cta_first[blockIdx.x + 1];
-    int pi = 0;
+    int pi = -1;
     while (rg < rg_end) {
         if (threadIdx.x == 0) {
             int q = pi;
-            while (q + 1 < nprob && rg_start[q + 1] <= rg) ++q;
+            if (q < 0) {
+                // the CTA's first problem: bisect (a scan from problem 0 is a chain of dependent global loads,
+                // 0.2 us each, that the CTAs of the last problems would pay before their first row)
+                int lo = 0, hi = nprob - 1;
+                while (lo < hi) {
+                    const int mid = (lo + hi + 1) >> 1;
+                    if (rg_start[mid] <= rg) lo = mid; else hi = mid - 1;
+                }
+                q = lo;
+            } else {
+                while (q + 1 < nprob && rg_start[q + 1] <= rg) ++q;
+            }
             s_prob = q;
         }
         __syncthreads();
