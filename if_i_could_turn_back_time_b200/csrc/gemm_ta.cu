@@ -244,15 +244,19 @@ __global__ void __launch_bounds__(kPrepThreads) ta_prepare_kernel(const TaProble
 // Tensor-memory columns: kRing slots per half of 64 columns each for the A operand (one 128-code group);
 // GF4 adds NB accumulator columns to every slot (one accumulator per group: the group's fp16 scale is
 // applied in fp32 after tcgen05.ld), E2M1 has one accumulator of NB columns per issuer for the whole row
-// (its scales are folded into the fp16 weights).  NB more columns carry the second half's sums to the
-// first half's threads at the end of a tile.
+// (its scales are folded into the fp16 weights).  The second half's sums reach the first half's threads at
+// the end of a tile through NB more columns (GF4) or through shared memory (E2M1, which needs all 512
+// columns at 32 and 64 rows).
 //
 // Where the time goes (clock64 counters per role, 11008 x 4096 GF4 and 8192 x 8192 E2M1, 16 batch rows): the
 // decode threads are busy decoding for about 60 % of a tile (GF4: the shared-memory pipe, 80 wavefronts per
 // 128 codes of 32 rows, is 3/4 full while they do; E2M1: about 230 instructions per 128 codes and thread),
-// the rest goes to the table build, the accumulator read-back and the end of the tile; the MMA issuers are
-// idle most of the time and neither the weight ring nor the activation rings are waited for (deepening the
-// weight ring to four stages changed nothing).  With the MMAs left out E2M1 runs 17 % faster, GF4 7 %.
+// the rest goes to the table build, the accumulator read-back and the end of the tile; neither the weight
+// ring nor the activation rings are waited for (deepening the weight ring to four stages changed nothing).
+// The MMA issuers are single lanes running dependent scalar code beside two decode warps: while they still
+// divided their ring positions out of counters they were the bottleneck of E2M1 (busy 89 % of the time, half
+// of it bookkeeping; with the MMAs left out the kernel ran 17 % faster); with the positions carried along
+// E2M1 runs at that decode bound, and GF4's issuers idle 3/4 of the time.
 constexpr int kTaThreads = 12 * 32;
 template <int FMT, int NB>
 struct Cols {
