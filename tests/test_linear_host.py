@@ -91,3 +91,43 @@ def test_scratch_buffers_are_per_thread():
     t.join()
     del mine["probe"]
     assert seen["empty"] and seen["cache"] is not mine
+
+
+def test_grouped_plan_partitions_the_row_space_evenly():
+    """jq_grouped_plan is host-only: its partition of the concatenated row-group space into one contiguous range
+    per CTA can be checked without a GPU (fake, aligned device addresses; nothing is dereferenced).  Layout of the
+    plan: 8 header ints [magic, n, grid, largest K, rows per group, batch, format, ...], then the first row group
+    of every problem (n + 1 ints) and of every CTA (grid + 1 ints)."""
+    import ctypes
+    import numpy as np
+    from if_i_could_turn_back_time_b200 import _lib
+    lib = _lib.load()
+    shapes = [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)]
+    n = len(shapes) * 4
+    arr = (_lib.jq_problem * n)()
+    for i in range(n):
+        N, K = shapes[i % len(shapes)]
+        arr[i].qweight = 0x10000000 + i * 0x4000000
+        arr[i].scales = 0x20000000 + i * 0x400000
+        arr[i].x = 0x30000000
+        arr[i].y = 0x40000000
+        arr[i].N, arr[i].K, arr[i].g, arr[i].had_block = N, K, 32, 0
+    nbytes = lib.jq_grouped_plan_bytes(n)
+    plan = np.zeros((nbytes + 3) // 4, dtype=np.int32)
+    st = lib.jq_grouped_plan(_lib.JQ_FMT_E2M1, ctypes.byref(arr), n, 1, plan.ctypes.data, plan.nbytes)
+    assert st == 0, _lib.strerror(st)
+    grid, rows_per_group = int(plan[2]), int(plan[4])
+    assert int(plan[1]) == n and grid > 0 and rows_per_group > 0
+    rg_start = plan[8:8 + n + 1]
+    cta_first = plan[8 + n + 1:8 + n + 1 + grid + 1]
+    groups = [(-(-shapes[i % len(shapes)][0] // rows_per_group)) for i in range(n)]
+    assert list(np.diff(rg_start)) == groups
+    assert cta_first[0] == 0 and cta_first[-1] == rg_start[-1] and np.all(np.diff(cta_first) >= 0)
+    # cost of every CTA's range in row-group x K units: within two row groups of the mean
+    k_of = np.repeat([shapes[i % len(shapes)][1] for i in range(n)], groups)
+    cost = np.array([k_of[a:b].sum() for a, b in zip(cta_first[:-1], cta_first[1:])], dtype=np.float64)
+    assert abs(cost - cost.mean()).max() <= 2 * 11008
+    # a misaligned weight pointer is refused before anything else happens
+    arr[3].qweight += 8
+    st = lib.jq_grouped_plan(_lib.JQ_FMT_E2M1, ctypes.byref(arr), n, 1, plan.ctypes.data, plan.nbytes)
+    assert st != 0 and "align" in _lib.strerror(st)
