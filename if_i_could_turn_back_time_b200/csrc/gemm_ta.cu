@@ -1108,7 +1108,10 @@ using namespace jqta;
 // largest K, 0, 0, 0],
 // tile_start[n + 1], cta_first[grid + 1], padding to 64 bytes, TaProblem[n], padding to 64 bytes, CUtensorMap[n]
 static const int kTaMagic = 0x4a515441;
-static const double kTileCost = 384, kProblemCost = 2048;   // in codes of one row: fixed time per tile / per problem
+// fixed time per tile / per problem of the partition's cost model, in codes of one row.  Swept on the 7B-shaped
+// GF4 step (us per step on one GPU / for an eighth of it): bytes only 940 / 150.5; 384, 2048: 921.5 / 143.0;
+// 768, 4096: 910.1 / 141.3; 1408, 6144: 900.1 / 140.1; 2304, 8192: 943.3 / 143.9.
+static const double kTileCost = 1408, kProblemCost = 6144;
 static const int kTaHeader = 12;
 
 // MMA N: GF4 keeps one accumulator per group and slot (up to 16 columns); E2M1 one per half (up to 64)
