@@ -16,7 +16,6 @@ import torch
 
 from . import _lib
 from .pack import PackedWeight
-from .spec import QuantSpec
 
 _DT = {torch.float32: _lib.JQ_F32, torch.float16: _lib.JQ_F16, torch.bfloat16: _lib.JQ_BF16}
 MAX_GEMV_BATCH = 8
